@@ -1,0 +1,228 @@
+/*
+ * onellm_b200 — C ABI of the sm_100a kernels that replace oneLLM's kernel layer.
+ *
+ * Every entry point takes raw DEVICE pointers, explicit sizes and strides (in elements),
+ * a dtype tag and a CUDA stream (passed as void*, 0 = legacy default stream), launches
+ * asynchronously on that stream and returns an int status: 0 on success, negative on
+ * failure.  Nothing throws or exits across this boundary; onellm_last_error() returns the
+ * text of the calling thread's last failure.  Execution errors surface at the caller's
+ * next synchronisation, as they do behind the reference's launch* functions.
+ *
+ * Each declaration names the reference interface it replaces (path:line inside the
+ * oneLLM tree).  The C++ headers under include/onellm/ restate those interfaces with the
+ * reference's own signatures on top of this ABI.
+ *
+ * There is no CPU fallback: without a CUDA device these functions fail with
+ * ONELLM_ERR_CUDA.
+ */
+#ifndef ONELLM_B200_H
+#define ONELLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ONELLM_API __attribute__((visibility("default")))
+
+enum onellm_dtype { ONELLM_F32 = 0, ONELLM_F16 = 1 };
+
+enum onellm_status {
+    ONELLM_OK = 0,
+    ONELLM_ERR_ARG = -1,         /* null pointer, bad size, misaligned pointer or stride */
+    ONELLM_ERR_UNSUPPORTED = -2, /* shape or dtype outside what the kernels cover */
+    ONELLM_ERR_CUDA = -3,        /* CUDA runtime error (message has the text) */
+    ONELLM_ERR_WORKSPACE = -4,   /* caller's scratch buffer is missing or too small */
+    ONELLM_ERR_IO = -5,          /* weight file missing or of the wrong size */
+    ONELLM_ERR_STATE = -6,       /* call made in the wrong order (e.g. decode before prefill) */
+    ONELLM_ERR_COMM = -7         /* NCCL failure or time-out */
+};
+
+/* Layout of a projection weight. */
+enum onellm_wlayout {
+    ONELLM_W_KN = 0, /* [K_in, N_out] row-major: the reference's layer weights */
+    ONELLM_W_NK = 1  /* [N_out, K_in] row-major: tok_embeddings / output.weight ([vocab, hidden]) */
+};
+
+ONELLM_API const char* onellm_last_error(void);
+ONELLM_API int onellm_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Decode-step fused masked self-attention with RoPE.
+ * Replaces launchDecoderMaskedMHA / masked_MHA_kernel
+ * (src/kernels/decoder_masked_attn.h:7-14, src/kernels/decoder_masked_attn.cu:136-327).
+ *
+ *   q [B,H,D], k and v [B,Hkv,D]: the new token's projections; *_stride_b is the element
+ *     stride between batches (so the three may be views of one fused [B,H+2Hkv,D] buffer).
+ *   bias_q [H*D], bias_k [Hkv*D], bias_v [Hkv*D]: may be NULL.
+ *   k_cache, v_cache: ONE layer's cache; element (b, kv_head, row, d) lives at
+ *     b*cs_b + kv_head*cs_h + row*cs_s + d.  The reference kernel's [S,B,Hkv,D] order and the
+ *     layers' [B,Hkv,S,D] order are both expressible.
+ *   step: number of rows attended, the new one included.  q and k get bias then RoPE at
+ *     position rope_pos; k and v (+bias) are stored in row step-1; the output is
+ *     softmax(scale * q.K^T) V over rows 0..step-1.  Query head h reads KV head h / (H/Hkv).
+ *   step_dev: optional DEVICE int.  When non-NULL the kernel reads the step from it at run
+ *     time (so a captured CUDA graph can be replayed as the sequence grows); `step` must
+ *     then be an upper bound of that value, and the position used is
+ *     *step_dev + (rope_pos - step).
+ *   rot_dim, rope_base: rotary dimension and base, pairs (2i, 2i+1), angle
+ *     rope_pos / rope_base^(2i/rot_dim).
+ *   out [B,H,D] with batch stride out_stride_b.
+ *   workspace: device scratch of at least onellm_decode_attn_workspace_bytes(B,H,D,step)
+ *     bytes, 16-byte aligned; used when the rows are split across thread blocks.
+ *
+ * dtype F32 or F16 (F16 storage, fp32 arithmetic).  D*sizeof(T) must be one of
+ * 64, 128, 256, 512 bytes.  All pointers and strides must keep rows 16-byte aligned.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API size_t onellm_decode_attn_workspace_bytes(int B, int H, int D, int max_step);
+
+ONELLM_API int onellm_decode_attn(int dtype, const void* q, const void* k, const void* v,
+                                  long q_stride_b, long k_stride_b, long v_stride_b,
+                                  const void* bias_q, const void* bias_k, const void* bias_v,
+                                  void* k_cache, void* v_cache, long cs_b, long cs_h, long cs_s,
+                                  int B, int H, int Hkv, int D, int step, const int* step_dev,
+                                  int rope_pos, int rot_dim, float rope_base, float scale, void* out,
+                                  long out_stride_b, void* workspace, size_t workspace_bytes,
+                                  void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * RMSNorm in place: x <- gamma * x * rsqrt(mean(x^2) + eps), x [num_tokens, hidden].
+ * Replaces launchRMSNorm (src/kernels/rmsnorm_kernel.h:6-9, rmsnorm_kernel.cu:47-103).
+ * gamma has the dtype of x.  hidden*sizeof(T) must be a multiple of 16.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_rmsnorm(int dtype, void* x, const void* gamma, float eps, int num_tokens,
+                              int hidden, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused add-bias-residual + RMSNorm:
+ *     residual    <- decoder_out + residual + bias          (bias may be NULL)
+ *     decoder_out <- gamma * residual * rsqrt(mean(residual^2) + eps)
+ * Replaces launchFusedAddBiasResidualRMSNorm<T>
+ * (src/kernels/fused_addresidual_norm.h:4-12, fused_addresidual_norm.cu:51-141), with the
+ * two outputs the decoder code expects from it (src/layers/decoder/self_decoder.cpp:50-73).
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_add_residual_rmsnorm(int dtype, void* residual, void* decoder_out,
+                                           const void* bias, const void* gamma, float eps,
+                                           int num_tokens, int hidden, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Projection y[M,N] = x[M,K] . W  (fp32 accumulation, no bias).
+ * Replaces launchLinearGemm + cublasWrapper::Gemm
+ * (src/kernels/qkv_linear.h:9-14, qkv_linear.cu:8-65, cublas_wrapper.cc:45-90).
+ * w_layout selects [K,N] (layer weights) or [N,K] (LM head).  F16: tensor cores; M <= 64
+ * takes the weight-streaming path, larger M the tiled path.  F32: plain fp32 arithmetic.
+ * F16 constraints: [K,N] weights need K % 16 == 0 and N % 8 == 0; [N,K] weights K % 32 == 0.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_gemm(int dtype, const void* x, const void* W, void* y, int M, int N, int K,
+                           int w_layout, void* stream);
+
+/* Gate and up projections with SwiGLU applied on the way out:
+ *     out[M,I] = silu(x.Wg) * (x.Wu),   Wg, Wu [K,I]
+ * Replaces the gate GEMM, up GEMM and launchAct of LLaMAFFNLayer::forward
+ * (src/layers/ffn/ffn.cpp:62-66, src/kernels/activation_kernel.cu:10-32).  F16 only. */
+ONELLM_API int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, const void* Wu, void* out,
+                                  int M, int I, int K, void* stream);
+
+/* Standalone SwiGLU on input [tokens, 2, I] -> out [tokens, I].
+ * Replaces launchAct<T> (src/kernels/activation_kernel.h:2-3, activation_kernel.cu:10-32). */
+ONELLM_API int onellm_swiglu(int dtype, const void* input, void* out, int tokens, int inter,
+                             void* stream);
+
+/* Embedding gather: out[t,:] = table[ids[t],:], ids int32 [n_tokens], table [vocab, hidden].
+ * Replaces launchInputEmbedding (src/kernels/input_embedding.h:5-7, input_embedding.cu:7-40).
+ * Ids outside [0, vocab) produce a zero row and set *bad_id_flag (device int, may be NULL). */
+ONELLM_API int onellm_embedding(int dtype, const int* ids, void* out, const void* table, int n_tokens,
+                                int hidden, int vocab, int* bad_id_flag, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Row-wise top-K of logits [rows, vocab] (F32 or F16), values sorted descending, ties to
+ * the lower column.  out_val float [rows,K], out_id int32 [rows,K] (column index, or
+ * row*vocab + column when global_ids != 0 as the reference's beam-search kernel emits).
+ * Generalises launchTopKforBeamSearch (src/kernels/beamsearch_topK.h:35-38,
+ * beamsearch_topK.cu:20-119), whose K is fixed at 2.  1 <= K <= 64.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_topk(int dtype, const void* logits, int rows, int vocab, int K, float* out_val,
+                           int* out_id, int global_ids, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Top-K sampling from sorted candidates.
+ * Replaces launchSampling / SamplingKernel (src/kernels/topK_sampling.h:9-14,
+ * topK_sampling.cu:6-70): w_i = exp((val_i - val_0)/temperature); u = curand_uniform of an
+ * XORWOW state initialised with (seed = rng_step, subsequence = row, offset = 0); walk the
+ * candidates subtracting w_i from u*sum(w) until it goes negative; id = topk_id % vocab_size;
+ * seqlen[b] += !finished[b]; finished[b] = (id == end_id).
+ * literal_walk != 0 reproduces the shipped walk (subtracts w_0 every time).
+ * topk_val is NOT modified (the reference overwrites it with the weights).
+ * seqlen / finished (bool bytes) may be NULL.  u_out (float [B], may be NULL) receives the
+ * uniform draws.  rng_step_dev: optional DEVICE int read at run time in place of rng_step
+ * (for replay inside a captured CUDA graph).
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_topk_sample(const int* topk_id, const float* topk_val, int B, int K,
+                                  float temperature, int rng_step, const int* rng_step_dev,
+                                  int vocab_size, int end_id, int literal_walk, int* output_id,
+                                  int* seqlen, unsigned char* finished, float* u_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * LLaMA model: weights, KV cache and the generation loop (host side in C++).
+ * Fills in the model class the reference leaves empty (src/models/llama/llama.h, outline in
+ * src/models/llama/llama.cpp:1-50) with the kernel order of LlamaSelfDecoder::forward
+ * (src/layers/decoder/self_decoder.cpp:15-78).  fp16 weights and activations.
+ * ------------------------------------------------------------------------------------- */
+typedef struct onellm_llama onellm_llama;
+
+typedef struct onellm_llama_config {
+    int num_layers, hidden, head_num, kv_head_num, head_size, inter_size, vocab_size;
+    int max_seq_len, max_batch; /* KV cache is [L, max_batch, kv_head_num/tp, max_seq_len, head_size] */
+    float rope_base;            /* <= 0: 10000 */
+    int rot_dim;                /* <= 0: head_size */
+    float rms_eps;              /* <= 0: 1e-5 */
+    int bos_id, eos_id;
+    int attn_bias;              /* qkv / o biases present (src/weights/llama/layer_weights.cc:26-29) */
+    int tp_rank, tp_size;       /* tensor parallel slice held by this process */
+} onellm_llama_config;
+
+ONELLM_API int onellm_llama_create(const onellm_llama_config* cfg, onellm_llama** out);
+ONELLM_API void onellm_llama_destroy(onellm_llama* m);
+ONELLM_API size_t onellm_llama_device_bytes(const onellm_llama* m);
+ONELLM_API void* onellm_llama_stream(onellm_llama* m);
+
+/* Weights from the reference's .bin files: `weight_path` is the prefix the reference's
+ * LlamaWeight::loadWeights takes (src/weights/llama/llama_weights.cc:36-46): files
+ * <p>.norm.weight, <p>.tok_embeddings.weight, <p>.output.weight,
+ * <p>layers.<l>.{attention_norm,ffn_norm}.weight, .attention.w_qkv.weight, .attention.wo.weight,
+ * .feed_forward.{w1,w3,w2}.weight (+ .attention.w_qkv.bias / .attention.wo.bias).  fp32 or fp16
+ * files; each rank keeps its tensor-parallel slice.  Missing / wrongly sized file: ONELLM_ERR_IO. */
+ONELLM_API int onellm_llama_load_weights(onellm_llama* m, const char* weight_path);
+/* Random weights ~N(0, std), gammas 1, generated on the device; identical for every tp_size. */
+ONELLM_API int onellm_llama_init_random(onellm_llama* m, uint64_t seed, float std);
+
+/* Tensor parallel: rank 0 creates the id, every rank passes the same 128 bytes. */
+ONELLM_API int onellm_nccl_unique_id(void* id128);
+ONELLM_API int onellm_llama_init_comm(onellm_llama* m, const void* id128);
+
+ONELLM_API int onellm_llama_set_sampling(onellm_llama* m, int top_k, float temperature, int literal_walk);
+ONELLM_API int onellm_llama_set_graphs(onellm_llama* m, int enabled);
+
+/* Context phase for `batch` prompts of equal length (host ids [batch, prompt_len]); resets the
+ * sequence state.  host_first_ids (may be NULL) receives the first generated token per prompt. */
+ONELLM_API int onellm_llama_prefill(onellm_llama* m, const int* host_ids, int batch, int prompt_len,
+                                    int* host_first_ids);
+/* One generated token per sequence.  host_in_ids (may be NULL: use the previous step's samples)
+ * are the tokens to feed; host_out_ids (may be NULL: stay asynchronous) receives the samples. */
+ONELLM_API int onellm_llama_decode_step(onellm_llama* m, const int* host_in_ids, int* host_out_ids);
+ONELLM_API int onellm_llama_sync(onellm_llama* m);
+/* prefill + n_new - 1 decode steps; host_out [batch, n_new]. */
+ONELLM_API int onellm_llama_generate(onellm_llama* m, const int* host_prompt, int batch, int prompt_len,
+                                     int n_new, int* host_out);
+/* Logits of the last step as float [batch, vocab_size] on the host. */
+ONELLM_API int onellm_llama_get_logits(onellm_llama* m, float* host_logits);
+ONELLM_API int onellm_llama_get_state(onellm_llama* m, int* cur_len, long* kernel_launches, int* host_seqlen,
+                                      unsigned char* host_finished);
+ONELLM_API int onellm_llama_kv_cache(onellm_llama* m, int layer, void** k_cache, void** v_cache);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ONELLM_B200_H */

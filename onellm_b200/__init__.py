@@ -1,0 +1,235 @@
+"""onellm_b200: sm_100a kernels and a LLaMA decode engine behind oneLLM's kernel interface.
+
+This module is a thin ctypes binding of ``libonellm_b200.so`` (see ``include/onellm_b200.h``)
+for the tests and the benchmark.  It does no arithmetic itself and has no fallback: if the
+library is missing, or a call fails, it raises.  Device buffers are passed as integer
+addresses (``torch.Tensor.data_ptr()``); the caller owns them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libonellm_b200.so")
+
+F32, F16 = 0, 1
+W_KN, W_NK = 0, 1
+
+_lib = None
+
+
+class OnellmError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"onellm_b200 status {status}: {message}")
+        self.status = status
+
+
+class LlamaConfig(C.Structure):
+    _fields_ = [
+        ("num_layers", C.c_int), ("hidden", C.c_int), ("head_num", C.c_int), ("kv_head_num", C.c_int),
+        ("head_size", C.c_int), ("inter_size", C.c_int), ("vocab_size", C.c_int),
+        ("max_seq_len", C.c_int), ("max_batch", C.c_int),
+        ("rope_base", C.c_float), ("rot_dim", C.c_int), ("rms_eps", C.c_float),
+        ("bos_id", C.c_int), ("eos_id", C.c_int), ("attn_bias", C.c_int),
+        ("tp_rank", C.c_int), ("tp_size", C.c_int),
+    ]
+
+
+def lib() -> C.CDLL:
+    """Loads the CUDA library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise OnellmError(-100, f"{LIB_PATH} is missing: run `python -m onellm_b200.build` "
+                                    "(there is no CPU fallback)")
+        l = C.CDLL(LIB_PATH)
+        l.onellm_last_error.restype = C.c_char_p
+        l.onellm_decode_attn_workspace_bytes.restype = C.c_size_t
+        l.onellm_llama_device_bytes.restype = C.c_size_t
+        l.onellm_llama_stream.restype = C.c_void_p
+        l.onellm_llama_destroy.restype = None
+        _lib = l
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise OnellmError(rc, lib().onellm_last_error().decode())
+
+
+def _p(x):
+    """Device/host address -> c_void_p (None -> NULL)."""
+    if x is None:
+        return C.c_void_p(0)
+    if hasattr(x, "data_ptr"):
+        return C.c_void_p(x.data_ptr())
+    return C.c_void_p(int(x))
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return C.c_void_p(int(stream))
+
+
+def decode_attn_workspace_bytes(B, H, D, max_step):
+    return int(lib().onellm_decode_attn_workspace_bytes(C.c_int(B), C.c_int(H), C.c_int(D), C.c_int(max_step)))
+
+
+def decode_attn(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache,
+                cs_b, cs_h, cs_s, B, H, Hkv, D, step, rope_pos, rot_dim, rope_base, scale, out, out_stride_b,
+                workspace, workspace_bytes, step_dev=None, stream=None):
+    _check(lib().onellm_decode_attn(
+        C.c_int(dtype), _p(q), _p(k), _p(v), C.c_long(q_stride_b), C.c_long(k_stride_b), C.c_long(v_stride_b),
+        _p(bias_q), _p(bias_k), _p(bias_v), _p(k_cache), _p(v_cache), C.c_long(cs_b), C.c_long(cs_h),
+        C.c_long(cs_s), C.c_int(B), C.c_int(H), C.c_int(Hkv), C.c_int(D), C.c_int(step), _p(step_dev),
+        C.c_int(rope_pos), C.c_int(rot_dim), C.c_float(rope_base), C.c_float(scale), _p(out),
+        C.c_long(out_stride_b), _p(workspace), C.c_size_t(workspace_bytes), _stream(stream)))
+
+
+def rmsnorm(dtype, x, gamma, eps, num_tokens, hidden, stream=None):
+    _check(lib().onellm_rmsnorm(C.c_int(dtype), _p(x), _p(gamma), C.c_float(eps), C.c_int(num_tokens),
+                                C.c_int(hidden), _stream(stream)))
+
+
+def add_residual_rmsnorm(dtype, residual, decoder_out, bias, gamma, eps, num_tokens, hidden, stream=None):
+    _check(lib().onellm_add_residual_rmsnorm(C.c_int(dtype), _p(residual), _p(decoder_out), _p(bias), _p(gamma),
+                                             C.c_float(eps), C.c_int(num_tokens), C.c_int(hidden),
+                                             _stream(stream)))
+
+
+def gemm(dtype, x, W, y, M, N, K, w_layout=W_KN, stream=None):
+    _check(lib().onellm_gemm(C.c_int(dtype), _p(x), _p(W), _p(y), C.c_int(M), C.c_int(N), C.c_int(K),
+                             C.c_int(w_layout), _stream(stream)))
+
+
+def gemm_swiglu(dtype, x, Wg, Wu, out, M, I, K, stream=None):
+    _check(lib().onellm_gemm_swiglu(C.c_int(dtype), _p(x), _p(Wg), _p(Wu), _p(out), C.c_int(M), C.c_int(I),
+                                    C.c_int(K), _stream(stream)))
+
+
+def swiglu(dtype, inp, out, tokens, inter, stream=None):
+    _check(lib().onellm_swiglu(C.c_int(dtype), _p(inp), _p(out), C.c_int(tokens), C.c_int(inter),
+                               _stream(stream)))
+
+
+def embedding(dtype, ids, out, table, n_tokens, hidden, vocab, bad_id_flag=None, stream=None):
+    _check(lib().onellm_embedding(C.c_int(dtype), _p(ids), _p(out), _p(table), C.c_int(n_tokens),
+                                  C.c_int(hidden), C.c_int(vocab), _p(bad_id_flag), _stream(stream)))
+
+
+def topk(dtype, logits, rows, vocab, K, out_val, out_id, global_ids=False, stream=None):
+    _check(lib().onellm_topk(C.c_int(dtype), _p(logits), C.c_int(rows), C.c_int(vocab), C.c_int(K),
+                             _p(out_val), _p(out_id), C.c_int(1 if global_ids else 0), _stream(stream)))
+
+
+def topk_sample(topk_id, topk_val, B, K, temperature, rng_step, vocab_size, end_id, output_id, seqlen=None,
+                finished=None, u_out=None, literal_walk=False, rng_step_dev=None, stream=None):
+    _check(lib().onellm_topk_sample(_p(topk_id), _p(topk_val), C.c_int(B), C.c_int(K), C.c_float(temperature),
+                                    C.c_int(rng_step), _p(rng_step_dev), C.c_int(vocab_size), C.c_int(end_id),
+                                    C.c_int(1 if literal_walk else 0), _p(output_id), _p(seqlen), _p(finished),
+                                    _p(u_out), _stream(stream)))
+
+
+def nccl_unique_id() -> bytes:
+    buf = C.create_string_buffer(128)
+    _check(lib().onellm_nccl_unique_id(buf))
+    return buf.raw
+
+
+class Llama:
+    """Host-side handle of the C++ model (weights, KV cache, generation loop)."""
+
+    def __init__(self, *, num_layers, hidden, head_num, kv_head_num, head_size, inter_size, vocab_size,
+                 max_seq_len, max_batch, rope_base=10000.0, rot_dim=0, rms_eps=1e-5, bos_id=1, eos_id=2,
+                 attn_bias=False, tp_rank=0, tp_size=1):
+        self.cfg = LlamaConfig(num_layers, hidden, head_num, kv_head_num, head_size, inter_size, vocab_size,
+                               max_seq_len, max_batch, rope_base, rot_dim, rms_eps, bos_id, eos_id,
+                               1 if attn_bias else 0, tp_rank, tp_size)
+        self._h = C.c_void_p(0)
+        _check(lib().onellm_llama_create(C.byref(self.cfg), C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().onellm_llama_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def device_bytes(self):
+        return int(lib().onellm_llama_device_bytes(self._h))
+
+    @property
+    def stream(self):
+        return int(lib().onellm_llama_stream(self._h) or 0)
+
+    def load_weights(self, prefix: str):
+        _check(lib().onellm_llama_load_weights(self._h, prefix.encode()))
+
+    def init_random(self, seed: int, std: float = 0.02):
+        _check(lib().onellm_llama_init_random(self._h, C.c_uint64(seed), C.c_float(std)))
+
+    def init_comm(self, unique_id: bytes):
+        _check(lib().onellm_llama_init_comm(self._h, C.c_char_p(unique_id)))
+
+    def set_sampling(self, top_k=1, temperature=1.0, literal_walk=False):
+        _check(lib().onellm_llama_set_sampling(self._h, C.c_int(top_k), C.c_float(temperature),
+                                               C.c_int(1 if literal_walk else 0)))
+
+    def set_graphs(self, enabled: bool):
+        _check(lib().onellm_llama_set_graphs(self._h, C.c_int(1 if enabled else 0)))
+
+    def prefill(self, ids):
+        """ids: int32 numpy [batch, prompt_len]; returns the first sampled id per sequence."""
+        import numpy as np
+        ids = np.ascontiguousarray(ids, np.int32)
+        out = np.zeros(ids.shape[0], np.int32)
+        _check(lib().onellm_llama_prefill(self._h, ids.ctypes.data_as(C.c_void_p), C.c_int(ids.shape[0]),
+                                          C.c_int(ids.shape[1]), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def decode_step(self, in_ids=None, out_ids=None):
+        """in_ids / out_ids: int32 numpy [batch] or None (see onellm_llama_decode_step)."""
+        _check(lib().onellm_llama_decode_step(
+            self._h, None if in_ids is None else in_ids.ctypes.data_as(C.c_void_p),
+            None if out_ids is None else out_ids.ctypes.data_as(C.c_void_p)))
+
+    def decode_step_raw(self, in_ptr: int, out_ptr: int):
+        """Same with raw host addresses (e.g. pinned torch tensors)."""
+        _check(lib().onellm_llama_decode_step(self._h, C.c_void_p(in_ptr), C.c_void_p(out_ptr)))
+
+    def sync(self):
+        _check(lib().onellm_llama_sync(self._h))
+
+    def generate(self, prompt, n_new):
+        import numpy as np
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        out = np.zeros((prompt.shape[0], n_new), np.int32)
+        _check(lib().onellm_llama_generate(self._h, prompt.ctypes.data_as(C.c_void_p), C.c_int(prompt.shape[0]),
+                                           C.c_int(prompt.shape[1]), C.c_int(n_new),
+                                           out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def logits(self, batch):
+        import numpy as np
+        out = np.zeros((batch, self.cfg.vocab_size), np.float32)
+        _check(lib().onellm_llama_get_logits(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def state(self):
+        cur = C.c_int(0)
+        launches = C.c_long(0)
+        _check(lib().onellm_llama_get_state(self._h, C.byref(cur), C.byref(launches), None, None))
+        return cur.value, launches.value
+
+    def kv_cache_ptrs(self, layer):
+        k, v = C.c_void_p(0), C.c_void_p(0)
+        _check(lib().onellm_llama_kv_cache(self._h, C.c_int(layer), C.byref(k), C.byref(v)))
+        return k.value, v.value

@@ -1,0 +1,456 @@
+// Decode-step fused masked self-attention with RoPE for sm_100a: split-KV, HBM-bound.
+//
+// Replaces masked_MHA_kernel (src/kernels/decoder_masked_attn.cu:136-268 of the reference).
+//
+// Work split: grid = (n_split, H / G, B).  A thread block owns G query heads that share one
+// KV head and one contiguous chunk of cached rows.  Inside the block a "lane group" of LPR
+// lanes owns a row at a time: each lane holds 16 bytes of the row (8 halfs / 4 floats), so one
+// warp load instruction fetches whole 128-byte lines; U rows of K and of V are in flight per
+// lane group before the first is consumed.  Scores are reduced with xor-shuffles over the
+// LPR lanes, the softmax is the running (max, sum) form kept in registers in the log2
+// domain, and the V accumulator stays in registers.  Lane groups are merged through shared
+// memory; splits are merged by a second, tiny kernel reading fp32 partials from scratch.
+//
+// The block that owns the last chunk also adds bias to the new k / v, rotates k, stores both
+// in cache row step-1 and attends to them from registers, so no other block ever reads a row
+// that is being written.  The RoPE denominators base^(2i/rot_dim) come in as kernel
+// parameters computed by the host's powf, so the angle pos / denom is the same float the
+// reference's CPU arithmetic produces.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace onellm {
+
+constexpr int kMaxRopePairs = 128;     // D <= 256
+constexpr int kAttnThreads = 128;      // 4 warps
+constexpr int kRowsInFlight = 4;       // U
+constexpr int kMinChunkRows = 64;
+
+struct DecodeAttnParams {
+    const void *q, *k, *v;
+    long q_sb, k_sb, v_sb;
+    const void *bq, *bk, *bv;
+    void *kc, *vc;
+    long cs_b, cs_h, cs_s;
+    int B, H, Hkv, D;
+    int step;
+    const int* step_dev;
+    int rope_delta;  // position = step + rope_delta
+    int rot_dim;
+    float scale_log2e;
+    void* out;
+    long out_sb;
+    float* part_acc;  // [B, H, n_split, D]
+    float* part_ml;   // [B, H, n_split, 2]
+    int n_split;      // grid.x
+    int chunk;        // rows per split
+    float rope_denom[kMaxRopePairs];
+};
+
+__device__ __forceinline__ int effective_splits(int n_cached, int chunk)
+{
+    const int s = (n_cached + chunk - 1) / chunk;
+    return s < 1 ? 1 : s;
+}
+
+template <typename T, int LPR, int G>
+__global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeAttnParams p)
+{
+    constexpr int VEC = Vec16<T>::N;
+    constexpr int D = LPR * VEC;
+    constexpr int GPW = 32 / LPR;                      // lane groups per warp
+    constexpr int NG = (kAttnThreads / 32) * GPW;      // lane groups per block
+    constexpr int U = kRowsInFlight;
+
+    const int split = blockIdx.x;
+    const int h0 = blockIdx.y * G;  // first query head of this block
+    const int b = blockIdx.z;
+    const int qpk = p.H / p.Hkv;
+    const int hk = h0 / qpk;
+    const bool writes_cache = (h0 % qpk) == 0;
+
+    const int step = p.step_dev ? *p.step_dev : p.step;
+    const float pos = (float)(step + p.rope_delta);
+    const int n_cached = step - 1;
+    const int n_split = effective_splits(n_cached, p.chunk);
+    if (split >= n_split) return;
+    const bool owns_new = (split == n_split - 1);
+    const int row0 = split * p.chunk;
+    const int row1 = min(row0 + p.chunk, n_cached);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = warp * GPW + lane / LPR;
+    const int d0 = (lane % LPR) * VEC;
+
+    // rotation coefficients for this lane's pairs
+    float cs[VEC / 2], sn[VEC / 2];
+#pragma unroll
+    for (int i = 0; i < VEC / 2; i++) {
+        const int d = d0 + 2 * i;
+        if (d < p.rot_dim) {
+            const float ang = pos / p.rope_denom[d >> 1];
+            sincosf(ang, &sn[i], &cs[i]);
+        } else {
+            cs[i] = 1.f;
+            sn[i] = 0.f;
+        }
+    }
+
+    // q: bias, rotate
+    float qf[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        Vec16<T>::load(reinterpret_cast<const T*>(p.q) + b * p.q_sb + (long)(h0 + g) * D + d0, qf[g]);
+        if (p.bq) {
+            float bb[VEC];
+            Vec16<T>::load(reinterpret_cast<const T*>(p.bq) + (long)(h0 + g) * D + d0, bb);
+#pragma unroll
+            for (int i = 0; i < VEC; i++) qf[g][i] += bb[i];
+        }
+#pragma unroll
+        for (int i = 0; i < VEC / 2; i++) {
+            const float x = qf[g][2 * i], y = qf[g][2 * i + 1];
+            qf[g][2 * i] = cs[i] * x - sn[i] * y;
+            qf[g][2 * i + 1] = cs[i] * y + sn[i] * x;
+        }
+    }
+
+    float m[G], l[G], acc[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; i++) acc[g][i] = 0.f;
+    }
+
+    const T* kc = reinterpret_cast<const T*>(p.kc) + b * p.cs_b + hk * p.cs_h + d0;
+    const T* vc = reinterpret_cast<const T*>(p.vc) + b * p.cs_b + hk * p.cs_h + d0;
+
+    // the trip count is the same for every lane group, so the shuffles below are warp-wide
+    for (int rbase = row0; rbase < row1; rbase += NG * U) {
+        const int r = rbase + grp;
+        uint4 kk[U], vv[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int rr = r + u * NG;
+            if (rr < row1) {
+                kk[u] = ld_nc_16(kc + (long)rr * p.cs_s);
+                vv[u] = ld_nc_16(vc + (long)rr * p.cs_s);
+            } else {
+                kk[u] = make_uint4(0, 0, 0, 0);
+                vv[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float s[U][G];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float kf[VEC];
+            Vec16<T>::unpack(kk[u], kf);
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < VEC; i++) a = fmaf(qf[g][i], kf[i], a);
+                s[u][g] = a;
+            }
+        }
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+                for (int g = 0; g < G; g++) s[u][g] += __shfl_xor_sync(0xffffffffu, s[u][g], o);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const bool valid = (r + u * NG) < row1;
+#pragma unroll
+            for (int g = 0; g < G; g++) s[u][g] = valid ? s[u][g] * p.scale_log2e : -INFINITY;
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float mn = m[g];
+#pragma unroll
+            for (int u = 0; u < U; u++) mn = fmaxf(mn, s[u][g]);
+            // a lane group that has seen no valid row yet keeps m = -inf; subtract 0 then, so
+            // that every exponent below is -inf (weight 0) instead of inf - inf
+            const float ms = (mn == -INFINITY) ? 0.f : mn;
+            const float corr = fast_exp2(m[g] - ms);
+            m[g] = mn;
+            l[g] *= corr;
+#pragma unroll
+            for (int i = 0; i < VEC; i++) acc[g][i] *= corr;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const float pr = fast_exp2(s[u][g] - ms);
+                l[g] += pr;
+                float vf[VEC];
+                Vec16<T>::unpack(vv[u], vf);
+#pragma unroll
+                for (int i = 0; i < VEC; i++) acc[g][i] = fmaf(pr, vf[i], acc[g][i]);
+            }
+        }
+    }
+
+    // the new token's row: lane group 0 of the block that owns the last chunk
+    if (owns_new && grp == 0) {
+        // only lanes 0..LPR-1 of warp 0 are here
+        constexpr unsigned kGroup0Mask = (LPR == 32) ? 0xffffffffu : ((1u << LPR) - 1u);
+        float kf[VEC], vf[VEC];
+        Vec16<T>::load(reinterpret_cast<const T*>(p.k) + b * p.k_sb + (long)hk * D + d0, kf);
+        Vec16<T>::load(reinterpret_cast<const T*>(p.v) + b * p.v_sb + (long)hk * D + d0, vf);
+        if (p.bk) {
+            float bb[VEC];
+            Vec16<T>::load(reinterpret_cast<const T*>(p.bk) + (long)hk * D + d0, bb);
+#pragma unroll
+            for (int i = 0; i < VEC; i++) kf[i] += bb[i];
+        }
+        if (p.bv) {
+            float bb[VEC];
+            Vec16<T>::load(reinterpret_cast<const T*>(p.bv) + (long)hk * D + d0, bb);
+#pragma unroll
+            for (int i = 0; i < VEC; i++) vf[i] += bb[i];
+        }
+#pragma unroll
+        for (int i = 0; i < VEC / 2; i++) {
+            const float x = kf[2 * i], y = kf[2 * i + 1];
+            kf[2 * i] = cs[i] * x - sn[i] * y;
+            kf[2 * i + 1] = cs[i] * y + sn[i] * x;
+        }
+        // attend to exactly what later steps will read back: the stored (rounded) values
+        const uint4 kp = Vec16<T>::pack(kf), vp = Vec16<T>::pack(vf);
+        if (writes_cache) {
+            T* kd = reinterpret_cast<T*>(p.kc) + b * p.cs_b + hk * p.cs_h + (long)(step - 1) * p.cs_s + d0;
+            T* vd = reinterpret_cast<T*>(p.vc) + b * p.cs_b + hk * p.cs_h + (long)(step - 1) * p.cs_s + d0;
+            *reinterpret_cast<uint4*>(kd) = kp;
+            *reinterpret_cast<uint4*>(vd) = vp;
+        }
+        Vec16<T>::unpack(kp, kf);
+        Vec16<T>::unpack(vp, vf);
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; i++) a = fmaf(qf[g][i], kf[i], a);
+#pragma unroll
+            for (int o = LPR / 2; o > 0; o >>= 1) a += __shfl_xor_sync(kGroup0Mask, a, o);
+            a *= p.scale_log2e;
+            const float mn = fmaxf(m[g], a);
+            const float corr = fast_exp2(m[g] - mn);
+            const float pr = fast_exp2(a - mn);
+            m[g] = mn;
+            l[g] = l[g] * corr + pr;
+#pragma unroll
+            for (int i = 0; i < VEC; i++) acc[g][i] = fmaf(pr, vf[i], acc[g][i] * corr);
+        }
+    }
+
+    // merge the lane groups of this block
+    __shared__ float sm_acc[NG][G][D];
+    __shared__ float sm_m[NG][G], sm_l[NG][G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+#pragma unroll
+        for (int i = 0; i < VEC; i++) sm_acc[grp][g][d0 + i] = acc[g][i];
+        if ((lane % LPR) == 0) {
+            sm_m[grp][g] = m[g];
+            sm_l[grp][g] = l[g];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += kAttnThreads) {
+        const int g = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < NG; i++) M = fmaxf(M, sm_m[i][g]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            const float w = fast_exp2(sm_m[i][g] - M);  // empty groups: exp2(-inf) = 0
+            L = fmaf(sm_l[i][g], w, L);
+            O = fmaf(sm_acc[i][g][d], w, O);
+        }
+        const int h = h0 + g;
+        if (n_split == 1) {
+            reinterpret_cast<T*>(p.out)[b * p.out_sb + (long)h * D + d] = (T)(O / L);
+        } else {
+            const long base = ((long)b * p.H + h) * p.n_split + split;
+            p.part_acc[base * D + d] = O;
+            if (d == 0) {
+                p.part_ml[base * 2] = M;
+                p.part_ml[base * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// Merges the per-split partials: out = sum_i O_i 2^(m_i - M) / sum_i L_i 2^(m_i - M).
+template <typename T>
+__global__ void decode_attn_combine_kernel(const DecodeAttnParams p)
+{
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int step = p.step_dev ? *p.step_dev : p.step;
+    const int n_split = effective_splits(step - 1, p.chunk);
+    if (n_split == 1) return;  // the attention kernel wrote the output itself
+    const long base = ((long)b * p.H + h) * p.n_split;
+    float M = -INFINITY;
+    for (int i = 0; i < n_split; i++) M = fmaxf(M, p.part_ml[(base + i) * 2]);
+    float L = 0.f;
+    for (int i = 0; i < n_split; i++)
+        L = fmaf(p.part_ml[(base + i) * 2 + 1], fast_exp2(p.part_ml[(base + i) * 2] - M), L);
+    const float invL = 1.f / L;
+    for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
+        float O = 0.f;
+        for (int i = 0; i < n_split; i++)
+            O = fmaf(p.part_acc[(base + i) * p.D + d], fast_exp2(p.part_ml[(base + i) * 2] - M), O);
+        reinterpret_cast<T*>(p.out)[b * p.out_sb + (long)h * p.D + d] = (T)(O * invL);
+    }
+}
+
+// Rows per split and number of splits for `step` rows: enough blocks to keep about eight
+// 128-thread blocks resident per SM, but never chunks shorter than kMinChunkRows.
+static int wanted_splits(int B, int n_head_blocks, int step)
+{
+    const int n_cached = step > 1 ? step - 1 : 0;
+    const int target_blocks = num_sms() * 8;
+    int want = (target_blocks + B * n_head_blocks - 1) / (B * n_head_blocks);
+    int max_split = (n_cached + kMinChunkRows - 1) / kMinChunkRows;
+    if (max_split < 1) max_split = 1;
+    if (want > max_split) want = max_split;
+    if (want < 1) want = 1;
+    return want;  // the plan below never uses more splits than this
+}
+
+static void plan_splits(int B, int n_head_blocks, int step, int* n_split, int* chunk)
+{
+    const int n_cached = step > 1 ? step - 1 : 0;
+    const int want = wanted_splits(B, n_head_blocks, step);
+    int c = (n_cached + want - 1) / want;
+    const int gran = 32;  // whole passes of every lane group
+    c = (c + gran - 1) / gran * gran;
+    if (c < kMinChunkRows) c = kMinChunkRows;
+    int s = (n_cached + c - 1) / c;
+    if (s < 1) s = 1;
+    *n_split = s;
+    *chunk = c;
+}
+
+static int pick_group(int qpk)
+{
+    if (qpk % 8 == 0) return 8;
+    if (qpk % 4 == 0) return 4;
+    if (qpk % 2 == 0) return 2;
+    return 1;
+}
+
+template <typename T, int LPR>
+static void launch_decode_attn(const DecodeAttnParams& p, int G, cudaStream_t st)
+{
+    const dim3 grid(p.n_split, p.H / G, p.B), block(kAttnThreads);
+    switch (G) {
+        case 8: decode_attn_kernel<T, LPR, 8><<<grid, block, 0, st>>>(p); break;
+        case 4: decode_attn_kernel<T, LPR, 4><<<grid, block, 0, st>>>(p); break;
+        case 2: decode_attn_kernel<T, LPR, 2><<<grid, block, 0, st>>>(p); break;
+        default: decode_attn_kernel<T, LPR, 1><<<grid, block, 0, st>>>(p); break;
+    }
+    if (p.n_split > 1) decode_attn_combine_kernel<T><<<dim3(p.H, p.B), 128, 0, st>>>(p);
+}
+
+}  // namespace onellm
+
+using namespace onellm;
+
+extern "C" size_t onellm_decode_attn_workspace_bytes(int B, int H, int D, int max_step)
+{
+    if (B <= 0 || H <= 0 || D <= 0 || max_step <= 0) return 0;
+    // upper bound over the head groupings the launcher may pick (1, 2, 4 or 8 heads per block)
+    size_t worst = 0;
+    for (int hb = 1; hb <= 8; hb *= 2) {
+        const int ns = wanted_splits(B, (H + hb - 1) / hb, max_step);
+        const size_t bytes = (size_t)B * H * ns * (D + 2) * sizeof(float);
+        if (bytes > worst) worst = bytes;
+    }
+    return worst + 256;
+}
+
+extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const void* v, long q_stride_b,
+                                  long k_stride_b, long v_stride_b, const void* bias_q,
+                                  const void* bias_k, const void* bias_v, void* k_cache, void* v_cache,
+                                  long cs_b, long cs_h, long cs_s, int B, int H, int Hkv, int D, int step,
+                                  const int* step_dev, int rope_pos, int rot_dim, float rope_base,
+                                  float scale, void* out, long out_stride_b, void* workspace,
+                                  size_t workspace_bytes, void* stream)
+{
+    ONELLM_REQUIRE(q && k && v && k_cache && v_cache && out, ONELLM_ERR_ARG, "decode_attn: null pointer");
+    ONELLM_REQUIRE(B > 0 && H > 0 && Hkv > 0 && D > 0 && step > 0, ONELLM_ERR_ARG,
+                   "decode_attn: non-positive size (B=%d H=%d Hkv=%d D=%d step=%d)", B, H, Hkv, D, step);
+    ONELLM_REQUIRE(H % Hkv == 0, ONELLM_ERR_ARG, "decode_attn: H=%d is not a multiple of Hkv=%d", H, Hkv);
+    const size_t es = dtype_size(dtype);
+    ONELLM_REQUIRE(es != 0, ONELLM_ERR_UNSUPPORTED, "decode_attn: dtype %d", dtype);
+    const size_t row_bytes = (size_t)D * es;
+    ONELLM_REQUIRE(row_bytes == 64 || row_bytes == 128 || row_bytes == 256 || row_bytes == 512,
+                   ONELLM_ERR_UNSUPPORTED, "decode_attn: head row of %zu bytes (need 64/128/256/512)",
+                   row_bytes);
+    ONELLM_REQUIRE(rot_dim >= 0 && rot_dim / 2 <= kMaxRopePairs && rope_base > 0.f, ONELLM_ERR_ARG,
+                   "decode_attn: bad rotary parameters");
+    const long vec = (long)(16 / es);
+    ONELLM_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(k_cache) && aligned16(v_cache) &&
+                       aligned16(out) && (!bias_q || aligned16(bias_q)) && (!bias_k || aligned16(bias_k)) &&
+                       (!bias_v || aligned16(bias_v)),
+                   ONELLM_ERR_ARG, "decode_attn: pointers must be 16-byte aligned");
+    ONELLM_REQUIRE(q_stride_b % vec == 0 && k_stride_b % vec == 0 && v_stride_b % vec == 0 &&
+                       cs_b % vec == 0 && cs_h % vec == 0 && cs_s % vec == 0 && out_stride_b % vec == 0,
+                   ONELLM_ERR_ARG, "decode_attn: strides must keep rows 16-byte aligned");
+
+    DecodeAttnParams p;
+    p.q = q; p.k = k; p.v = v;
+    p.q_sb = q_stride_b; p.k_sb = k_stride_b; p.v_sb = v_stride_b;
+    p.bq = bias_q; p.bk = bias_k; p.bv = bias_v;
+    p.kc = k_cache; p.vc = v_cache;
+    p.cs_b = cs_b; p.cs_h = cs_h; p.cs_s = cs_s;
+    p.B = B; p.H = H; p.Hkv = Hkv; p.D = D;
+    p.step = step;
+    p.step_dev = step_dev;
+    p.rope_delta = rope_pos - step;
+    p.rot_dim = rot_dim < D ? rot_dim : D;
+    p.scale_log2e = scale * 1.4426950408889634f;
+    p.out = out;
+    p.out_sb = out_stride_b;
+    for (int i = 0; i < kMaxRopePairs; i++)
+        p.rope_denom[i] = (2 * i < p.rot_dim) ? powf(rope_base, (float)(2 * i) / (float)rot_dim) : 1.f;
+
+    const int G = pick_group(H / Hkv);
+    plan_splits(B, H / G, step, &p.n_split, &p.chunk);
+    p.part_acc = nullptr;
+    p.part_ml = nullptr;
+    if (p.n_split > 1) {
+        const size_t need_acc = (size_t)B * H * p.n_split * D * sizeof(float);
+        const size_t need = need_acc + (size_t)B * H * p.n_split * 2 * sizeof(float);
+        ONELLM_REQUIRE(workspace && aligned16(workspace) && workspace_bytes >= need, ONELLM_ERR_WORKSPACE,
+                       "decode_attn: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+        p.part_acc = reinterpret_cast<float*>(workspace);
+        p.part_ml = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + need_acc);
+    }
+    ONELLM_REQUIRE(B <= 65535 && H / G <= 65535, ONELLM_ERR_UNSUPPORTED, "decode_attn: grid too large");
+
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int lpr = (int)(row_bytes / 16);
+    if (dtype == ONELLM_F16) {
+        switch (lpr) {
+            case 4: launch_decode_attn<__half, 4>(p, G, st); break;
+            case 8: launch_decode_attn<__half, 8>(p, G, st); break;
+            case 16: launch_decode_attn<__half, 16>(p, G, st); break;
+            default: launch_decode_attn<__half, 32>(p, G, st); break;
+        }
+    } else {
+        switch (lpr) {
+            case 4: launch_decode_attn<float, 4>(p, G, st); break;
+            case 8: launch_decode_attn<float, 8>(p, G, st); break;
+            case 16: launch_decode_attn<float, 16>(p, G, st); break;
+            default: launch_decode_attn<float, 32>(p, G, st); break;
+        }
+    }
+    ONELLM_CHECK_LAUNCH();
+    return ONELLM_OK;
+}

