@@ -209,6 +209,9 @@ ONELLM_API int onellm_llama_set_graphs(onellm_llama* m, int enabled);
  * sequence state.  host_first_ids (may be NULL) receives the first generated token per prompt. */
 ONELLM_API int onellm_llama_prefill(onellm_llama* m, const int* host_ids, int batch, int prompt_len,
                                     int* host_first_ids);
+/* Declares cur_len positions of `batch` sequences as already present in the KV cache and host_ids
+ * [batch] as the next input tokens (resume on a cache filled elsewhere; profiling without prefill). */
+ONELLM_API int onellm_llama_seek(onellm_llama* m, int batch, int cur_len, const int* host_ids);
 /* One generated token per sequence.  host_in_ids (may be NULL: use the previous step's samples)
  * are the tokens to feed; host_out_ids (may be NULL: stay asynchronous) receives the samples. */
 ONELLM_API int onellm_llama_decode_step(onellm_llama* m, const int* host_in_ids, int* host_out_ids);

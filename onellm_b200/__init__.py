@@ -195,6 +195,11 @@ class Llama:
                                           C.c_int(ids.shape[1]), out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def seek(self, batch, cur_len, ids):
+        import numpy as np
+        ids = np.ascontiguousarray(ids, np.int32)
+        _check(lib().onellm_llama_seek(self._h, C.c_int(batch), C.c_int(cur_len), ids.ctypes.data_as(C.c_void_p)))
+
     def decode_step(self, in_ids=None, out_ids=None):
         """in_ids / out_ids: int32 numpy [batch] or None (see onellm_llama_decode_step)."""
         _check(lib().onellm_llama_decode_step(

@@ -119,6 +119,56 @@ __device__ __forceinline__ uint4 ld_nc_16(const void* p)
     return r;
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+constexpr int kMaxStages = 26;
+// wait_group takes an immediate; the ring depth is chosen per launch, hence the switch
+__device__ __forceinline__ void cp_async_wait_dyn(int pending)
+{
+    switch (pending) {
+#define ONELLM_W(n) case n: cp_async_wait<n>(); break;
+        ONELLM_W(0) ONELLM_W(1) ONELLM_W(2) ONELLM_W(3) ONELLM_W(4) ONELLM_W(5) ONELLM_W(6) ONELLM_W(7) ONELLM_W(8)
+        ONELLM_W(9) ONELLM_W(10) ONELLM_W(11) ONELLM_W(12) ONELLM_W(13) ONELLM_W(14) ONELLM_W(15) ONELLM_W(16)
+        ONELLM_W(17) ONELLM_W(18) ONELLM_W(19) ONELLM_W(20) ONELLM_W(21) ONELLM_W(22) ONELLM_W(23)
+#undef ONELLM_W
+        default: cp_async_wait<24>(); break;
+    }
+}
+// Programmatic dependent launch.  A kernel launched with launch_pdl() may start while the
+// kernel before it in the stream is still running; pdl_wait() blocks until that kernel has
+// completed and its writes are visible, so everything that reads (or overwrites) data the
+// previous kernel touches must come after it.  EVERY kernel of a chain calls pdl_wait() once,
+// also when it has nothing to wait for: completion is only transitive through the waits.
+// pdl_launch_dependents() lets the next kernel begin its own independent prologue early.
+// Both are no-ops in a kernel that was launched normally.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float fast_exp2(float x)
 {
     float y;

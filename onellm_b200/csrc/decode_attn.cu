@@ -18,13 +18,17 @@
 // reference's CPU arithmetic produces.
 #include <math.h>
 
+#include <map>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace onellm {
 
 constexpr int kMaxRopePairs = 128;     // D <= 256
 constexpr int kAttnThreads = 128;      // 4 warps
-constexpr int kRowsInFlight = 4;       // U
+constexpr int kRowsPerGroup = 2;       // U: rows a lane group takes from one stage
+constexpr int kAttnStageBytes = 8192;  // K and V rows of one stage (always 256 + 256 chunks of 16 bytes)
 constexpr int kMinChunkRows = 64;
 
 struct DecodeAttnParams {
@@ -45,6 +49,7 @@ struct DecodeAttnParams {
     float* part_ml;   // [B, H, n_split, 2]
     int n_split;      // grid.x
     int chunk;        // rows per split
+    int nst;          // depth of the shared-memory ring
     float rope_denom[kMaxRopePairs];
 };
 
@@ -61,7 +66,9 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
     constexpr int D = LPR * VEC;
     constexpr int GPW = 32 / LPR;                      // lane groups per warp
     constexpr int NG = (kAttnThreads / 32) * GPW;      // lane groups per block
-    constexpr int U = kRowsInFlight;
+    constexpr int U = kRowsPerGroup;
+    constexpr int SR = NG * U;                         // rows per stage
+    constexpr int ROWB = LPR * 16;                     // bytes per row
 
     const int split = blockIdx.x;
     const int h0 = blockIdx.y * G;  // first query head of this block
@@ -74,7 +81,11 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
     const float pos = (float)(step + p.rope_delta);
     const int n_cached = step - 1;
     const int n_split = effective_splits(n_cached, p.chunk);
-    if (split >= n_split) return;
+    if (split >= n_split) {
+        pdl_launch_dependents();
+        pdl_wait();
+        return;
+    }
     const bool owns_new = (split == n_split - 1);
     const int row0 = split * p.chunk;
     const int row1 = min(row0 + p.chunk, n_cached);
@@ -97,6 +108,49 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
         }
     }
 
+    float m[G], l[G], acc[G][VEC];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; i++) acc[g][i] = 0.f;
+    }
+
+    // K/V rows come through a ring of shared-memory stages filled by 16-byte cp.async copies
+    // (each warp-wide copy covers whole 128-byte lines), so the bytes in flight per SM are set
+    // by the ring depth, not by registers.  A stage holds SR rows of K, then SR rows of V.
+    extern __shared__ __align__(16) unsigned char ring[];
+    const uint32_t ring_base = (uint32_t)__cvta_generic_to_shared(ring);
+    const T* kc = reinterpret_cast<const T*>(p.kc) + b * p.cs_b + hk * p.cs_h;
+    const T* vc = reinterpret_cast<const T*>(p.vc) + b * p.cs_b + hk * p.cs_h;
+    const int n_iter = row1 > row0 ? (row1 - row0 + SR - 1) / SR : 0;
+    const int nst = p.nst;
+    auto issue = [&](int it, int buf) {
+        if (it < n_iter) {
+            const int r0 = row0 + it * SR;
+            const uint32_t sb = ring_base + (uint32_t)(buf * kAttnStageBytes);
+#pragma unroll
+            for (int i = 0; i < (SR * LPR) / kAttnThreads; i++) {
+                const int c = threadIdx.x + kAttnThreads * i;
+                const int row = c / LPR, ch = c % LPR;
+                const int rr = r0 + row;
+                const bool ok = rr < row1;
+                const long off = ok ? (long)rr * p.cs_s + ch * VEC : 0;
+                cp_async16(sb + row * ROWB + ch * 16, kc + off, ok ? 16 : 0);
+                cp_async16(sb + (SR + row) * ROWB + ch * 16, vc + off, ok ? 16 : 0);
+            }
+        }
+        cp_async_commit();
+    };
+    for (int s = 0; s < nst - 1; s++) issue(s, s);
+    int buf = 0, fill = nst - 1;
+
+    // Nothing above reads what the previous kernel in the stream wrote (cache rows below
+    // step-1 are older than that); q, k and v do.  The next kernel is released after the main
+    // loop: released earlier, its blocks would take residency this kernel's single wave needs.
+    pdl_wait();
+
     // q: bias, rotate
     float qf[G][VEC];
 #pragma unroll
@@ -116,32 +170,22 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
         }
     }
 
-    float m[G], l[G], acc[G][VEC];
-#pragma unroll
-    for (int g = 0; g < G; g++) {
-        m[g] = -INFINITY;
-        l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < VEC; i++) acc[g][i] = 0.f;
-    }
 
-    const T* kc = reinterpret_cast<const T*>(p.kc) + b * p.cs_b + hk * p.cs_h + d0;
-    const T* vc = reinterpret_cast<const T*>(p.vc) + b * p.cs_b + hk * p.cs_h + d0;
-
-    // the trip count is the same for every lane group, so the shuffles below are warp-wide
-    for (int rbase = row0; rbase < row1; rbase += NG * U) {
-        const int r = rbase + grp;
+    // the trip count is the same for every thread: the barrier and the shuffles below are safe
+    for (int it = 0; it < n_iter; it++) {
+        cp_async_wait_dyn(nst - 2);
+        __syncthreads();
+        issue(it + nst - 1, fill);
+        const unsigned char* sb = ring + buf * kAttnStageBytes;
+        buf = buf + 1 == nst ? 0 : buf + 1;
+        fill = fill + 1 == nst ? 0 : fill + 1;
+        const int r = row0 + it * SR + grp;
         uint4 kk[U], vv[U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
-            const int rr = r + u * NG;
-            if (rr < row1) {
-                kk[u] = ld_nc_16(kc + (long)rr * p.cs_s);
-                vv[u] = ld_nc_16(vc + (long)rr * p.cs_s);
-            } else {
-                kk[u] = make_uint4(0, 0, 0, 0);
-                vv[u] = make_uint4(0, 0, 0, 0);
-            }
+            const int srow = grp + u * NG;
+            kk[u] = *reinterpret_cast<const uint4*>(sb + srow * ROWB + (lane % LPR) * 16);
+            vv[u] = *reinterpret_cast<const uint4*>(sb + (SR + srow) * ROWB + (lane % LPR) * 16);
         }
         float s[U][G];
 #pragma unroll
@@ -192,6 +236,9 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
             }
         }
     }
+
+    cp_async_wait<0>();
+    pdl_launch_dependents();
 
     // the new token's row: lane group 0 of the block that owns the last chunk
     if (owns_new && grp == 0) {
@@ -289,6 +336,8 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
 template <typename T>
 __global__ void decode_attn_combine_kernel(const DecodeAttnParams p)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
     const int step = p.step_dev ? *p.step_dev : p.step;
     const int n_split = effective_splits(step - 1, p.chunk);
@@ -308,32 +357,76 @@ __global__ void decode_attn_combine_kernel(const DecodeAttnParams p)
     }
 }
 
-// Rows per split and number of splits for `step` rows: enough blocks to keep about eight
-// 128-thread blocks resident per SM, but never chunks shorter than kMinChunkRows.
-static int wanted_splits(int B, int n_head_blocks, int step)
+constexpr int kMaxSplits = 32;
+
+// Upper bound on the splits any plan uses for `step` rows.
+static int max_splits(int step)
 {
     const int n_cached = step > 1 ? step - 1 : 0;
-    const int target_blocks = num_sms() * 8;
-    int want = (target_blocks + B * n_head_blocks - 1) / (B * n_head_blocks);
-    int max_split = (n_cached + kMinChunkRows - 1) / kMinChunkRows;
-    if (max_split < 1) max_split = 1;
-    if (want > max_split) want = max_split;
-    if (want < 1) want = 1;
-    return want;  // the plan below never uses more splits than this
+    int m = (n_cached + kMinChunkRows - 1) / kMinChunkRows;
+    if (m < 1) m = 1;
+    return m > kMaxSplits ? kMaxSplits : m;
 }
 
-static void plan_splits(int B, int n_head_blocks, int step, int* n_split, int* chunk)
+struct AttnPlan {
+    int n_split, chunk, nst;
+    size_t dyn_smem;
+};
+
+// Splits, rows per split and ring depth for `step` rows.
+//   regs_per_sm : blocks per SM the kernel's registers allow
+//   static_smem : its static shared memory
+//   row_bytes   : bytes of one K (or V) row; a stage holds kAttnStageBytes of K+V rows
+// The bandwidth a launch reaches grows with the bytes it keeps in flight (resident blocks x
+// ring depth x stage size, bounded by shared memory); a last wave of blocks that is nearly
+// empty costs as much as a full one; every split adds partials to write and merge.  The
+// plan enumerates (blocks per SM, splits) and takes the cheapest by that model.
+static AttnPlan plan_attention(int B, int n_head_blocks, int step, int regs_per_sm, size_t static_smem,
+                               size_t row_bytes)
 {
     const int n_cached = step > 1 ? step - 1 : 0;
-    const int want = wanted_splits(B, n_head_blocks, step);
-    int c = (n_cached + want - 1) / want;
-    const int gran = 32;  // whole passes of every lane group
-    c = (c + gran - 1) / gran * gran;
-    if (c < kMinChunkRows) c = kMinChunkRows;
-    int s = (n_cached + c - 1) / c;
-    if (s < 1) s = 1;
-    *n_split = s;
-    *chunk = c;
+    const long base = (long)B * n_head_blocks;
+    const int ms = max_splits(step);
+    const int sms = num_sms();
+    const int stage_rows = (int)(kAttnStageBytes / (2 * row_bytes));
+    const double rows_per_us = 6.5e6 / (2.0 * (double)row_bytes);  // all blocks together, at peak
+    AttnPlan best = {1, kMinChunkRows, 2, 2 * (size_t)kAttnStageBytes};
+    double best_t = 1e30;
+    for (int r = regs_per_sm; r >= 1; r--) {
+        const long smem_block = (long)(227 * 1024) / r - (long)static_smem - 1024;
+        int nst_cap = (int)(smem_block / kAttnStageBytes);
+        if (nst_cap > kMaxStages) nst_cap = kMaxStages;
+        if (nst_cap < 2) continue;
+        const long slots = (long)r * sms;
+        for (int n = 1; n <= ms; n++) {
+            int c = (n_cached + n - 1) / n;
+            c = (c + 31) / 32 * 32;
+            if (c < kMinChunkRows) c = kMinChunkRows;
+            int ns = (n_cached + c - 1) / c;
+            if (ns < 1) ns = 1;
+            const long total = base * ns;
+            const long waves = (total + slots - 1) / slots;
+            const long resident = total < slots ? total : slots;
+            int nst = (c + stage_rows - 1) / stage_rows + 1;
+            if (nst > nst_cap) nst = nst_cap;
+            if (nst < 2) nst = 2;
+            const double inflight = (double)resident * (nst - 1) * kAttnStageBytes;
+            // share of peak bandwidth: bounded by the bytes in flight and by what one block can
+            // consume (about 11.5 GB/s measured: its softmax chain is latency-bound)
+            double bw = inflight / 28e6;
+            const double by_blocks = (double)resident * 11.5e3 / 6.5e6;
+            if (by_blocks < bw) bw = by_blocks;
+            bw = bw > 1.0 ? 1.0 : (bw < 0.02 ? 0.02 : bw);
+            // microseconds: streaming + per-block start-up per wave + merge of the partials
+            const double t = (double)waves * ((double)resident * c / (rows_per_us * bw) + 1.5) +
+                             (ns > 1 ? 2.5 + 0.05 * ns : 0.0);
+            if (t < best_t) {
+                best_t = t;
+                best = {ns, c, nst, (size_t)nst * kAttnStageBytes};
+            }
+        }
+    }
+    return best;
 }
 
 static int pick_group(int qpk)
@@ -344,17 +437,57 @@ static int pick_group(int qpk)
     return 1;
 }
 
+using AttnKernel = void (*)(const DecodeAttnParams);
+
 template <typename T, int LPR>
-static void launch_decode_attn(const DecodeAttnParams& p, int G, cudaStream_t st)
+static AttnKernel attn_kernel_for(int G)
 {
-    const dim3 grid(p.n_split, p.H / G, p.B), block(kAttnThreads);
     switch (G) {
-        case 8: decode_attn_kernel<T, LPR, 8><<<grid, block, 0, st>>>(p); break;
-        case 4: decode_attn_kernel<T, LPR, 4><<<grid, block, 0, st>>>(p); break;
-        case 2: decode_attn_kernel<T, LPR, 2><<<grid, block, 0, st>>>(p); break;
-        default: decode_attn_kernel<T, LPR, 1><<<grid, block, 0, st>>>(p); break;
+        case 8: return decode_attn_kernel<T, LPR, 8>;
+        case 4: return decode_attn_kernel<T, LPR, 4>;
+        case 2: return decode_attn_kernel<T, LPR, 2>;
+        default: return decode_attn_kernel<T, LPR, 1>;
     }
-    if (p.n_split > 1) decode_attn_combine_kernel<T><<<dim3(p.H, p.B), 128, 0, st>>>(p);
+}
+
+template <typename T>
+static AttnKernel attn_kernel_for(int lpr, int G)
+{
+    switch (lpr) {
+        case 4: return attn_kernel_for<T, 4>(G);
+        case 8: return attn_kernel_for<T, 8>(G);
+        case 16: return attn_kernel_for<T, 16>(G);
+        default: return attn_kernel_for<T, 32>(G);
+    }
+}
+
+struct AttnKernelInfo {
+    int blocks_per_sm_regs;  // residency allowed by registers and threads
+    size_t static_smem;
+};
+
+// Per-kernel facts the planner needs (queried once; also raises the dynamic shared-memory cap).
+static AttnKernelInfo kernel_info(AttnKernel k)
+{
+    static std::map<AttnKernel, AttnKernelInfo> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(k);
+    if (it != cache.end()) return it->second;
+    AttnKernelInfo info = {4, 4096};
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, k) == cudaSuccess) {
+        info.static_smem = fa.sharedSizeBytes;
+        int by_regs = fa.numRegs > 0 ? 65536 / (fa.numRegs * kAttnThreads) : 4;
+        if (by_regs > 2048 / kAttnThreads) by_regs = 2048 / kAttnThreads;
+        if (by_regs < 1) by_regs = 1;
+        info.blocks_per_sm_regs = by_regs;
+        (void)cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(227 * 1024 - fa.sharedSizeBytes));
+    }
+    (void)cudaGetLastError();
+    cache[k] = info;
+    return info;
 }
 
 }  // namespace onellm
@@ -364,13 +497,7 @@ using namespace onellm;
 extern "C" size_t onellm_decode_attn_workspace_bytes(int B, int H, int D, int max_step)
 {
     if (B <= 0 || H <= 0 || D <= 0 || max_step <= 0) return 0;
-    // upper bound over the head groupings the launcher may pick (1, 2, 4 or 8 heads per block)
-    size_t worst = 0;
-    for (int hb = 1; hb <= 8; hb *= 2) {
-        const int ns = wanted_splits(B, (H + hb - 1) / hb, max_step);
-        const size_t bytes = (size_t)B * H * ns * (D + 2) * sizeof(float);
-        if (bytes > worst) worst = bytes;
-    }
+    const size_t worst = (size_t)B * H * max_splits(max_step) * (D + 2) * sizeof(float);
     return worst + 256;
 }
 
@@ -421,7 +548,13 @@ extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const
         p.rope_denom[i] = (2 * i < p.rot_dim) ? powf(rope_base, (float)(2 * i) / (float)rot_dim) : 1.f;
 
     const int G = pick_group(H / Hkv);
-    plan_splits(B, H / G, step, &p.n_split, &p.chunk);
+    const int lpr = (int)(row_bytes / 16);
+    const AttnKernel kern = dtype == ONELLM_F16 ? attn_kernel_for<__half>(lpr, G) : attn_kernel_for<float>(lpr, G);
+    const AttnKernelInfo info = kernel_info(kern);
+    const AttnPlan plan = plan_attention(B, H / G, step, info.blocks_per_sm_regs, info.static_smem, row_bytes);
+    p.n_split = plan.n_split;
+    p.chunk = plan.chunk;
+    p.nst = plan.nst;
     p.part_acc = nullptr;
     p.part_ml = nullptr;
     if (p.n_split > 1) {
@@ -435,21 +568,12 @@ extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const
     ONELLM_REQUIRE(B <= 65535 && H / G <= 65535, ONELLM_ERR_UNSUPPORTED, "decode_attn: grid too large");
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const int lpr = (int)(row_bytes / 16);
-    if (dtype == ONELLM_F16) {
-        switch (lpr) {
-            case 4: launch_decode_attn<__half, 4>(p, G, st); break;
-            case 8: launch_decode_attn<__half, 8>(p, G, st); break;
-            case 16: launch_decode_attn<__half, 16>(p, G, st); break;
-            default: launch_decode_attn<__half, 32>(p, G, st); break;
-        }
-    } else {
-        switch (lpr) {
-            case 4: launch_decode_attn<float, 4>(p, G, st); break;
-            case 8: launch_decode_attn<float, 8>(p, G, st); break;
-            case 16: launch_decode_attn<float, 16>(p, G, st); break;
-            default: launch_decode_attn<float, 32>(p, G, st); break;
-        }
+    ONELLM_CUDA(launch_pdl(kern, dim3(p.n_split, H / G, B), dim3(kAttnThreads), plan.dyn_smem, st, p));
+    if (p.n_split > 1) {
+        if (dtype == ONELLM_F16)
+            ONELLM_CUDA(launch_pdl(decode_attn_combine_kernel<__half>, dim3(H, B), dim3(128), 0, st, p));
+        else
+            ONELLM_CUDA(launch_pdl(decode_attn_combine_kernel<float>, dim3(H, B), dim3(128), 0, st, p));
     }
     ONELLM_CHECK_LAUNCH();
     return ONELLM_OK;

@@ -75,9 +75,11 @@ static NcclApi& nccl_api()
 }
 
 // ---- small kernels of the model driver -------------------------------------------------------
+// First kernel of every step, launched with a full stream dependency: everything after it sees
+// the new step.
 __global__ void advance_step_kernel(int* step) { *step += 1; }
 
-// ids[b] = prompt[b * prompt_len + (*step - 1)]
+// ids[b] = prompt[b * prompt_len + (*step - 1)]; launched with a full stream dependency
 __global__ void gather_prompt_ids_kernel(const int* __restrict__ prompt, int prompt_len, const int* __restrict__ step,
                                          int* __restrict__ ids, int B)
 {
@@ -158,6 +160,7 @@ struct Llama {
     ncclComm_t comm = nullptr;
     long launches = 0;  // kernels enqueued by this model (graph replays count their nodes)
     std::map<long, int> graph_nodes;
+    std::map<long, int> warmed;  // keys whose first step already ran outside a capture
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -224,6 +227,12 @@ static int blocks_for(size_t n) { return (int)((n + 255) / 256 < 4096 ? (n + 255
 
 // elementwise.cu: out = silu(gate) * up over n elements (n a multiple of 8); out may alias gate
 int swiglu_pair_f16(const __half* gate, const __half* up, __half* out, size_t n, cudaStream_t st);
+int embedding_launch(int dtype, const int* ids, void* out, void* out2, const void* table, int n_tokens, int hidden,
+                     int vocab, int* bad_id_flag, bool pdl, cudaStream_t st);
+// sampling.cu
+int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, float temperature, int rng_step,
+                       const int* rng_step_dev, int vocab_size, int end_id, int literal_walk, int* output_id,
+                       int* seqlen, unsigned char* finished, float* u_out, int* output_id2, cudaStream_t st);
 
 #define RC(call)              \
     do {                      \
@@ -251,12 +260,15 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
     const int B = m.batch, h = c.hidden, D = c.head_size;
     cudaStream_t st = m.stream;
     void* sp = (void*)st;
+    // The step counter advances first.  This kernel, the id gather and the embedding are
+    // launched with full stream dependencies; every later kernel of the step may overlap its
+    // predecessor's tail (programmatic dependent launch) and therefore starts after these.
+    advance_step_kernel<<<1, 1, 0, st>>>(m.d_step);
     if (mode & MODE_GATHER) {
         gather_prompt_ids_kernel<<<(B + 127) / 128, 128, 0, st>>>(m.d_prompt, prompt_len, m.d_step, m.d_ids, B);
         m.launches++;
     }
-    RC(onellm_embedding(ONELLM_F16, m.d_ids, m.y, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, sp));
-    ONELLM_CUDA(cudaMemcpyAsync(m.res, m.y, (size_t)B * h * sizeof(__half), cudaMemcpyDeviceToDevice, st));
+    RC(embedding_launch(ONELLM_F16, m.d_ids, m.y, m.res, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
     RC(onellm_rmsnorm(ONELLM_F16, m.y, m.layers[0].attn_norm, c.rms_eps, B, h, sp));
     m.launches += 3;
     const long cs_b = (long)m.Hkvl * c.max_seq_len * D, cs_h = (long)c.max_seq_len * D, cs_s = D;
@@ -295,13 +307,10 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
     if (mode & MODE_HEAD) {
         RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));
         RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
-        RC(onellm_topk_sample(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size,
-                              c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, sp));
-        ONELLM_CUDA(cudaMemcpyAsync(m.d_ids, m.d_out_ids, (size_t)B * sizeof(int), cudaMemcpyDeviceToDevice, st));
-        m.launches += 4;
+        RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size,
+                              c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, st));
+        m.launches += 3;
     }
-    advance_step_kernel<<<1, 1, 0, st>>>(m.d_step);
-    m.launches++;
     ONELLM_CHECK_LAUNCH();
     return ONELLM_OK;
 }
@@ -311,6 +320,7 @@ static void drop_graphs(Llama& m)
     for (auto& kv : m.graphs) cudaGraphExecDestroy(kv.second);
     m.graphs.clear();
     m.graph_nodes.clear();
+    m.warmed.clear();
 }
 
 // Runs one step (attending cur_len + 1 rows) and advances cur_len.
@@ -329,6 +339,14 @@ static int run_step(Llama& m, int mode, int prompt_len)
     const long key = ((long)bound << 20) | ((long)m.batch << 8) | ((long)mode << 4) | (m.top_k > 1 ? 1 : 0);
     // prompt_len, top_k, temperature are baked into the captured nodes: changing them drops the cache
     auto it = m.graphs.find(key);
+    if (it == m.graphs.end() && !m.warmed.count(key)) {
+        // first step of this shape runs eagerly: the launch planners query occupancy and set
+        // function attributes once per kernel, which must not happen inside a stream capture
+        m.warmed[key] = 1;
+        RC(enqueue_step(m, mode, bound, prompt_len));
+        m.cur_len++;
+        return ONELLM_OK;
+    }
     if (it == m.graphs.end()) {
         const long before = m.launches;
         cudaGraph_t g = nullptr;
@@ -641,12 +659,12 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
     m->batch = batch;
     m->graph_prompt_len = prompt_len;
     m->cur_len = 0;
-    const int one = 1;
+    const int zero = 0;
     ONELLM_CUDA(cudaMemcpyAsync(m->d_prompt, host_ids, (size_t)batch * prompt_len * sizeof(int), cudaMemcpyHostToDevice, st));
-    ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &one, sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &zero, sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemsetAsync(m->d_seqlen, 0, (size_t)batch * sizeof(int), st));
     ONELLM_CUDA(cudaMemsetAsync(m->d_finished, 0, (size_t)batch, st));
-    ONELLM_CUDA(cudaStreamSynchronize(st));  // `one` lives on this stack frame
+    ONELLM_CUDA(cudaStreamSynchronize(st));  // `zero` lives on this stack frame
     // context phase, one position at a time through the decode kernels; only the last
     // position needs the LM head
     for (int p = 0; p < prompt_len; p++)
@@ -656,6 +674,29 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
     int bad = 0;
     ONELLM_CUDA(cudaMemcpy(&bad, m->d_bad_id, sizeof(int), cudaMemcpyDeviceToHost));
     ONELLM_REQUIRE(bad == 0, ONELLM_ERR_ARG, "llama_prefill: token id outside [0, vocab_size)");
+    return ONELLM_OK;
+}
+
+// Declares `cur_len` positions of `batch` sequences as already cached (whatever the cache holds)
+// and `host_ids` as the next input tokens: resumes decoding on a cache filled elsewhere, and lets
+// profiling runs skip the context phase.
+extern "C" int onellm_llama_seek(onellm_llama* h, int batch, int cur_len, const int* host_ids)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m && host_ids, ONELLM_ERR_ARG, "llama_seek: null pointer");
+    ONELLM_REQUIRE(m->weights_ready, ONELLM_ERR_STATE, "llama_seek: weights not loaded");
+    ONELLM_REQUIRE(batch >= 1 && batch <= m->c.max_batch && cur_len >= 1 && cur_len < m->c.max_seq_len, ONELLM_ERR_ARG,
+                   "llama_seek: batch or position out of range");
+    cudaStream_t st = m->stream;
+    ONELLM_CUDA(cudaStreamSynchronize(st));
+    if (batch != m->batch) drop_graphs(*m);
+    m->batch = batch;
+    m->cur_len = cur_len;
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &cur_len, sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_ids, host_ids, (size_t)batch * sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemsetAsync(m->d_seqlen, 0, (size_t)batch * sizeof(int), st));
+    ONELLM_CUDA(cudaMemsetAsync(m->d_finished, 0, (size_t)batch, st));
+    ONELLM_CUDA(cudaStreamSynchronize(st));
     return ONELLM_OK;
 }
 

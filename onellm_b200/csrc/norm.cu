@@ -40,6 +40,8 @@ rmsnorm_kernel(T* __restrict__ x, T* __restrict__ residual, const T* __restrict_
 {
     constexpr int VEC = Vec16<T>::N;
     const int nvec = hidden / VEC;
+    pdl_launch_dependents();
+    pdl_wait();
     T* xr = x + (size_t)blockIdx.x * hidden;
     T* rr = FUSED ? residual + (size_t)blockIdx.x * hidden : nullptr;
 
@@ -110,11 +112,11 @@ static void launch_norm(void* x, void* residual, const void* bias, const void* g
 {
     const int nvec = hidden / Vec16<T>::N;
     if (nvec <= kNormThreads * kMaxVec)
-        rmsnorm_kernel<T, FUSED, true><<<num_tokens, kNormThreads, 0, st>>>(
-            (T*)x, (T*)residual, (const T*)bias, (const T*)gamma, eps, hidden);
+        (void)launch_pdl(rmsnorm_kernel<T, FUSED, true>, dim3(num_tokens), dim3(kNormThreads), 0, st, (T*)x, (T*)residual,
+                         (const T*)bias, (const T*)gamma, eps, hidden);
     else
-        rmsnorm_kernel<T, FUSED, false><<<num_tokens, kNormThreads, 0, st>>>(
-            (T*)x, (T*)residual, (const T*)bias, (const T*)gamma, eps, hidden);
+        (void)launch_pdl(rmsnorm_kernel<T, FUSED, false>, dim3(num_tokens), dim3(kNormThreads), 0, st, (T*)x,
+                         (T*)residual, (const T*)bias, (const T*)gamma, eps, hidden);
 }
 
 static int check_norm_args(const char* who, int dtype, const void* x, const void* gamma, int num_tokens,

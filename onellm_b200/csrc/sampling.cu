@@ -44,6 +44,8 @@ __global__ void __launch_bounds__(kTopkThreads)
 topk_kernel(const T* __restrict__ logits, int vocab, int K, float* __restrict__ out_val, int* __restrict__ out_id,
             int global_ids)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x;
     const T* x = logits + (size_t)row * vocab;
     __shared__ int hist[256];
@@ -149,8 +151,11 @@ topk_kernel(const T* __restrict__ logits, int vocab, int K, float* __restrict__ 
 __global__ void sample_kernel(const int* __restrict__ topk_id, const float* __restrict__ topk_val, int K,
                               float temperature, int rng_step, const int* __restrict__ rng_step_dev,
                               int vocab_size, int end_id, int literal_walk, int* __restrict__ output_id, int* __restrict__ seqlen,
-                              unsigned char* __restrict__ finished, float* __restrict__ u_out)
+                              unsigned char* __restrict__ finished, float* __restrict__ u_out,
+                              int* __restrict__ output_id2)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x;
     if (threadIdx.x != 0) return;
     const float* v = topk_val + (size_t)b * K;
@@ -173,6 +178,7 @@ __global__ void sample_kernel(const int* __restrict__ topk_id, const float* __re
     }
     const int id = topk_id[(size_t)b * K + pick] % vocab_size;
     output_id[b] = id;
+    if (output_id2) output_id2[b] = id;
     if (seqlen && finished) {
         seqlen[b] = finished[b] ? seqlen[b] : seqlen[b] + 1;
         finished[b] = (id == end_id) ? 1 : 0;
@@ -193,19 +199,23 @@ extern "C" int onellm_topk(int dtype, const void* logits, int rows, int vocab, i
     if (rows == 0) return ONELLM_OK;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == ONELLM_F16)
-        topk_kernel<__half><<<rows, kTopkThreads, 0, st>>>((const __half*)logits, vocab, K, out_val, out_id, global_ids);
+        ONELLM_CUDA(launch_pdl(topk_kernel<__half>, dim3(rows), dim3(kTopkThreads), 0, st, (const __half*)logits, vocab, K,
+                               out_val, out_id, global_ids));
     else if (dtype == ONELLM_F32)
-        topk_kernel<float><<<rows, kTopkThreads, 0, st>>>((const float*)logits, vocab, K, out_val, out_id, global_ids);
+        ONELLM_CUDA(launch_pdl(topk_kernel<float>, dim3(rows), dim3(kTopkThreads), 0, st, (const float*)logits, vocab, K,
+                               out_val, out_id, global_ids));
     else
         ONELLM_REQUIRE(false, ONELLM_ERR_UNSUPPORTED, "topk: dtype %d", dtype);
     ONELLM_CHECK_LAUNCH();
     return ONELLM_OK;
 }
 
-extern "C" int onellm_topk_sample(const int* topk_id, const float* topk_val, int B, int K, float temperature,
-                                  int rng_step, const int* rng_step_dev, int vocab_size, int end_id,
-                                  int literal_walk, int* output_id, int* seqlen, unsigned char* finished,
-                                  float* u_out, void* stream)
+namespace onellm {
+// Shared by the C entry point and the model driver; output_id2 (may be NULL) gets a second
+// copy of the sampled ids (the next step's input buffer).
+int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, float temperature, int rng_step,
+                       const int* rng_step_dev, int vocab_size, int end_id, int literal_walk, int* output_id,
+                       int* seqlen, unsigned char* finished, float* u_out, int* output_id2, cudaStream_t st)
 {
     ONELLM_REQUIRE(topk_id && topk_val && output_id, ONELLM_ERR_ARG, "topk_sample: null pointer");
     ONELLM_REQUIRE(B >= 0 && K >= 1 && vocab_size > 0 && temperature > 0.f, ONELLM_ERR_ARG,
@@ -213,9 +223,19 @@ extern "C" int onellm_topk_sample(const int* topk_id, const float* topk_val, int
     ONELLM_REQUIRE((seqlen == nullptr) == (finished == nullptr), ONELLM_ERR_ARG,
                    "topk_sample: seqlen and finished must be given together");
     if (B == 0) return ONELLM_OK;
-    sample_kernel<<<B, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        topk_id, topk_val, K, temperature, rng_step, rng_step_dev, vocab_size, end_id, literal_walk, output_id,
-        seqlen, finished, u_out);
-    ONELLM_CHECK_LAUNCH();
+    ONELLM_CUDA(launch_pdl(sample_kernel, dim3(B), dim3(32), 0, st, topk_id, topk_val, K, temperature, rng_step,
+                           rng_step_dev, vocab_size, end_id, literal_walk, output_id, seqlen, finished, u_out,
+                           output_id2));
     return ONELLM_OK;
+}
+}  // namespace onellm
+
+extern "C" int onellm_topk_sample(const int* topk_id, const float* topk_val, int B, int K, float temperature,
+                                  int rng_step, const int* rng_step_dev, int vocab_size, int end_id,
+                                  int literal_walk, int* output_id, int* seqlen, unsigned char* finished,
+                                  float* u_out, void* stream)
+{
+    return topk_sample_launch(topk_id, topk_val, B, K, temperature, rng_step, rng_step_dev, vocab_size, end_id,
+                              literal_walk, output_id, seqlen, finished, u_out, nullptr,
+                              reinterpret_cast<cudaStream_t>(stream));
 }

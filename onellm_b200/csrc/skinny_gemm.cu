@@ -1,34 +1,19 @@
-// Decode-time projections (M <= 64 tokens) for sm_100a: weight-streaming, HBM-bound.
-//
-// Replaces the cuBLAS calls behind launchLinearGemm (src/kernels/qkv_linear.cu:8-65,
-// src/kernels/cublas_wrapper.cc:45-90) for the shapes of a decode step, and fuses the SwiGLU
-// of src/kernels/activation_kernel.cu:10-21 into the gate/up projection.
-//
-// At M <= 64 every weight is used for a handful of FMAs, so the kernel is judged on bytes per
-// second.  The weight matrix is read exactly once, straight from global memory into
-// registers with 16-byte loads, in the layout it has on disk and in the reference's weight
-// structs ([K, N], N contiguous); nothing is staged in shared memory.  The arithmetic runs on
-// the tensor cores as mma.m16n8k16 with the WEIGHT as the 16-row operand and the 8 tokens of a
-// batch block as the 8-column operand, so a batch of 8 wastes nothing.  Because a sum over k
-// does not care about the order of k, each lane may feed the k slots of its fragment from
-// whichever rows it loaded: lane (g, t) loads rows kb+4t .. kb+4t+3 at columns n0+8g .. +7 and
-// pairs halves of two rows with one byte-permute per register.  The activations are the
-// small operand and come through L1 as 8-byte loads.
-//
-// K is split over the warps of a block and over the blocks of a thread-block cluster; the
-// partial sums meet in distributed shared memory (no global scratch, no atomics, a fixed
-// summation order, so results are bitwise reproducible).
-#include <cooperative_groups.h>
+// Projection entry points (onellm_gemm, onellm_gemm_swiglu) and two of their kernels:
+//   - the LM head at decode time, y = x . W^T with W [N, K] (vocab rows, K contiguous), M <= 64;
+//   - a plain fp32 GEMM for callers that keep the reference's fp32 tensors.
+// The [K, N] weight-streaming kernel is in skinny_gemm_staged.cu, the tiled kernel for M > 64 in
+// gemm_tc.cu.  Replaces launchLinearGemm / cublasWrapper::Gemm (src/kernels/qkv_linear.cu:8-65,
+// src/kernels/cublas_wrapper.cc:45-90 of the reference).
+
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
-
-namespace cg = cooperative_groups;
 
 namespace onellm {
 
 constexpr int kSkinnyThreads = 128;  // 4 warps
-constexpr int kColsPerBlock = 64;
-constexpr int kRedStride = 65;       // floats per row of the reduction tile
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1)
@@ -40,139 +25,19 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
-
-// y[M,N] = x[M,K] . W[K,N]            (DUAL = false)
-// y[M,N] = silu(x.W0) * (x.W1)        (DUAL = true)
-// grid = (ceil(N/64), KS), cluster = (1, KS, 1); M <= 8*MB.
-template <int MB, bool DUAL, int UK>
-__global__ void __launch_bounds__(kSkinnyThreads)
-skinny_kn_kernel(const __half* __restrict__ x, const __half* __restrict__ W0, const __half* __restrict__ W1,
-                 __half* __restrict__ y, int M, int N, int K, int ksteps_per_block)
-{
-    constexpr int NW = DUAL ? 2 : 1;
-    constexpr int MP = 8 * MB;  // padded token count
-    cg::cluster_group cluster = cg::this_cluster();
-    const int KS = gridDim.y;
-    const int rank = blockIdx.y;
-    const int n0 = blockIdx.x * kColsPerBlock;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int col = n0 + 8 * g;
-    const bool col_ok = col < N;  // N is a multiple of 8
-    const int total_ksteps = K / 16;
-    const int ks_begin = rank * ksteps_per_block;
-    const int ks_end = min(ks_begin + ksteps_per_block, total_ksteps);
-
-    float acc[NW][MB][4][4];
-#pragma unroll
-    for (int w = 0; w < NW; w++)
-#pragma unroll
-        for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) acc[w][mb][i][e] = 0.f;
-
-    const __half* xrow[MB];
-#pragma unroll
-    for (int mb = 0; mb < MB; mb++) xrow[mb] = x + (size_t)min(8 * mb + g, M - 1) * K + 4 * t;
-    const __half* wbase[NW];
-    wbase[0] = W0 + (size_t)(4 * t) * N + col;
-    if (DUAL) wbase[NW - 1] = W1 + (size_t)(4 * t) * N + col;
-
-    for (int ks = ks_begin + warp; ks < ks_end; ks += 4 * UK) {
-        uint4 wr[NW][UK][4];
-        uint2 xb[UK][MB];
-#pragma unroll
-        for (int u = 0; u < UK; u++) {
-            const int ksu = ks + 4 * u;
-            const bool ok = ksu < ks_end;
-            const size_t kb = (size_t)ksu * 16;
-#pragma unroll
-            for (int w = 0; w < NW; w++)
-#pragma unroll
-                for (int j = 0; j < 4; j++)
-                    wr[w][u][j] = (ok && col_ok) ? ld_nc_16(wbase[w] + (kb + j) * N) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int mb = 0; mb < MB; mb++)
-                xb[u][mb] = ok ? __ldg(reinterpret_cast<const uint2*>(xrow[mb] + kb)) : make_uint2(0, 0);
-        }
-#pragma unroll
-        for (int u = 0; u < UK; u++)
-#pragma unroll
-            for (int w = 0; w < NW; w++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
-                    const uint32_t lo0 = (i < 2) ? wr[w][u][0].x : wr[w][u][0].y;
-                    const uint32_t lo1 = (i < 2) ? wr[w][u][1].x : wr[w][u][1].y;
-                    const uint32_t lo2 = (i < 2) ? wr[w][u][2].x : wr[w][u][2].y;
-                    const uint32_t lo3 = (i < 2) ? wr[w][u][3].x : wr[w][u][3].y;
-                    const uint32_t hi0 = (i < 2) ? wr[w][u][0].z : wr[w][u][0].w;
-                    const uint32_t hi1 = (i < 2) ? wr[w][u][1].z : wr[w][u][1].w;
-                    const uint32_t hi2 = (i < 2) ? wr[w][u][2].z : wr[w][u][2].w;
-                    const uint32_t hi3 = (i < 2) ? wr[w][u][3].z : wr[w][u][3].w;
-                    const uint32_t a0 = __byte_perm(lo0, lo1, sel);  // column 8g+i,   k slots 2t, 2t+1
-                    const uint32_t a2 = __byte_perm(lo2, lo3, sel);  // column 8g+i,   k slots 2t+8, 2t+9
-                    const uint32_t a1 = __byte_perm(hi0, hi1, sel);  // column 8g+4+i, k slots 2t, 2t+1
-                    const uint32_t a3 = __byte_perm(hi2, hi3, sel);  // column 8g+4+i, k slots 2t+8, 2t+9
-#pragma unroll
-                    for (int mb = 0; mb < MB; mb++) mma_16816(acc[w][mb][i], a0, a1, a2, a3, xb[u][mb].x, xb[u][mb].y);
-                }
-    }
-
-    // reduce the four warps into this block's tile: red[w][token][column]
-    extern __shared__ float red[];  // NW * MP * kRedStride floats
-    for (int wsel = 0; wsel < 4; wsel++) {
-        if (warp == wsel) {
-#pragma unroll
-            for (int w = 0; w < NW; w++)
-#pragma unroll
-                for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++)
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const int tok = 8 * mb + 2 * t + (e & 1);
-                            const int c = 8 * g + i + ((e & 2) ? 4 : 0);
-                            float* dst = &red[(w * MP + tok) * kRedStride + c];
-                            *dst = (wsel == 0) ? acc[w][mb][i][e] : *dst + acc[w][mb][i][e];
-                        }
-        }
-        __syncthreads();
-    }
-    cluster.sync();
-
-    // every block of the cluster finishes a slice of the tile, summing ranks in order
-    const int per_rank = (MP * kColsPerBlock + KS - 1) / KS;
-    const int e_begin = rank * per_rank;
-    const int e_end = min(e_begin + per_rank, MP * kColsPerBlock);
-    for (int e = e_begin + threadIdx.x; e < e_end; e += kSkinnyThreads) {
-        const int tok = e / kColsPerBlock, c = e % kColsPerBlock;
-        float s0 = 0.f, s1 = 0.f;
-        for (int r = 0; r < KS; r++) {
-            const float* peer = cluster.map_shared_rank(red, r);
-            s0 += peer[tok * kRedStride + c];
-            if (DUAL) s1 += peer[(MP + tok) * kRedStride + c];
-        }
-        if (tok < M && n0 + c < N) {
-            const float v = DUAL ? silu_f(s0) * s1 : s0;
-            y[(size_t)tok * N + n0 + c] = __float2half_rn(v);
-        }
-    }
-    cluster.sync();  // peers may still be reading this block's tile
-}
-
 // y[M,N] = x[M,K] . W^T with W [N, K] (K contiguous): the LM head.  Each warp owns 16 rows of W
 // and streams them contiguously, 64 bytes per row per load instruction; no byte-permutes are
-// needed because consecutive k are already adjacent.  grid = (ceil(N/64)), 4 warps x 16 rows.
+// needed because consecutive k are already adjacent.  Warps are independent, so the block size
+// (1, 2 or 4 warps of 16 rows) is picked per launch to fill whole waves.
 template <int MB, int UK>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_nk_kernel(const __half* __restrict__ x, const __half* __restrict__ W, __half* __restrict__ y, int M, int N,
                  int K)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.x * 64 + warp * 16;  // first W row of this warp
+    const int r0 = (blockIdx.x * (blockDim.x >> 5) + warp) * 16;  // first W row of this warp
     if (r0 >= N) return;
     const int ra = min(r0 + g, N - 1), rb = min(r0 + g + 8, N - 1);
     const __half* wa = W + (size_t)ra * K + 8 * t;
@@ -226,6 +91,7 @@ sgemm_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __
 {
     __shared__ float xs[16][64 + 1];
     __shared__ float ws[16][64 + 1];
+    pdl_wait();
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
     float acc[4][4] = {};
@@ -267,61 +133,61 @@ sgemm_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __
         }
 }
 
-static int pick_ksplit(int N, int K)
-{
-    const int col_blocks = (N + kColsPerBlock - 1) / kColsPerBlock;
-    const int target = num_sms() * 4;
-    int ks = 1;
-    while (ks < 8 && col_blocks * ks < target && K / (ks * 2) >= 4 * 16 * 2) ks *= 2;
-    return ks;
-}
+// skinny_gemm_staged.cu
+cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
+                                      int K, bool dual, cudaStream_t st);
 
-template <int MB, bool DUAL, int UK>
-static cudaError_t launch_skinny_kn(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
-                                    int K, cudaStream_t st)
-{
-    const int KS = pick_ksplit(N, K);
-    const int total_ksteps = K / 16;
-    const int per_block = (total_ksteps + KS - 1) / KS;
-    const size_t smem = (size_t)(DUAL ? 2 : 1) * 8 * MB * kRedStride * sizeof(float);
-    auto kern = skinny_kn_kernel<MB, DUAL, UK>;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + kColsPerBlock - 1) / kColsPerBlock, KS, 1);
-    cfg.blockDim = dim3(kSkinnyThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = KS;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, per_block);
-}
-
-// one pass of at most 64 tokens
 static cudaError_t skinny_kn_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
                                       int K, bool dual, cudaStream_t st)
 {
-    if (dual) {
-        if (M <= 8) return launch_skinny_kn<1, true, 2>(x, W0, W1, y, M, N, K, st);
-        if (M <= 16) return launch_skinny_kn<2, true, 2>(x, W0, W1, y, M, N, K, st);
-        return launch_skinny_kn<4, true, 1>(x, W0, W1, y, M, N, K, st);
+    return skinny_kn_staged_dispatch(x, W0, W1, y, M, N, K, dual, st);
+}
+
+template <int MB, int UK>
+static void launch_skinny_nk(const __half* x, const __half* W, __half* y, int M, int N, int K, cudaStream_t st)
+{
+    auto kern = skinny_nk_kernel<MB, UK>;
+    static int best_warps[3] = {0, 0, 0};  // residency per block size, queried once
+    static std::mutex mu;
+    int per_sm[3];
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < 3; i++) {
+            if (best_warps[i] == 0) {
+                int n = 0;
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, 32 << i, 0) != cudaSuccess || n < 1) {
+                    (void)cudaGetLastError();
+                    n = 4;
+                }
+                best_warps[i] = n;
+            }
+            per_sm[i] = best_warps[i];
+        }
     }
-    if (M <= 8) return launch_skinny_kn<1, false, 4>(x, W0, nullptr, y, M, N, K, st);
-    if (M <= 16) return launch_skinny_kn<2, false, 4>(x, W0, nullptr, y, M, N, K, st);
-    if (M <= 32) return launch_skinny_kn<4, false, 2>(x, W0, nullptr, y, M, N, K, st);
-    return launch_skinny_kn<8, false, 2>(x, W0, nullptr, y, M, N, K, st);
+    const int tasks = (N + 15) / 16;  // one warp each
+    int pick = 2;
+    double best = -1.0;
+    for (int i = 0; i < 3; i++) {
+        const int warps = 1 << i;
+        const long blocks = (tasks + warps - 1) / warps;
+        const long slots = (long)per_sm[i] * num_sms();
+        const long waves = (blocks + slots - 1) / slots;
+        const double eff = (double)blocks / (double)(waves * slots) + 0.01 * i;  // ties: larger blocks
+        if (eff > best) {
+            best = eff;
+            pick = i;
+        }
+    }
+    const int warps = 1 << pick;
+    (void)launch_pdl(kern, dim3((tasks + warps - 1) / warps), dim3(32 * warps), 0, st, x, W, y, M, N, K);
 }
 
 static void skinny_nk_dispatch(const __half* x, const __half* W, __half* y, int M, int N, int K, cudaStream_t st)
 {
-    const dim3 grid((N + 63) / 64), block(kSkinnyThreads);
-    if (M <= 8) skinny_nk_kernel<1, 4><<<grid, block, 0, st>>>(x, W, y, M, N, K);
-    else if (M <= 16) skinny_nk_kernel<2, 4><<<grid, block, 0, st>>>(x, W, y, M, N, K);
-    else if (M <= 32) skinny_nk_kernel<4, 2><<<grid, block, 0, st>>>(x, W, y, M, N, K);
-    else skinny_nk_kernel<8, 2><<<grid, block, 0, st>>>(x, W, y, M, N, K);
+    if (M <= 8) launch_skinny_nk<1, 4>(x, W, y, M, N, K, st);
+    else if (M <= 16) launch_skinny_nk<2, 4>(x, W, y, M, N, K, st);
+    else if (M <= 32) launch_skinny_nk<4, 2>(x, W, y, M, N, K, st);
+    else launch_skinny_nk<8, 2>(x, W, y, M, N, K, st);
 }
 
 // Defined in gemm_tc.cu: the tiled tensor-core path for M > 64.
@@ -382,8 +248,8 @@ extern "C" int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, cons
     ONELLM_REQUIRE(x && Wg && Wu && out, ONELLM_ERR_ARG, "gemm_swiglu: null pointer");
     ONELLM_REQUIRE(M >= 0 && I > 0 && K > 0, ONELLM_ERR_ARG, "gemm_swiglu: bad size");
     ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "gemm_swiglu: only F16 is implemented");
-    ONELLM_REQUIRE(M <= 32, ONELLM_ERR_UNSUPPORTED,
-                   "gemm_swiglu: fused path covers M <= 32; use two projections and onellm_swiglu");
+    ONELLM_REQUIRE(M <= 64, ONELLM_ERR_UNSUPPORTED,
+                   "gemm_swiglu: fused path covers M <= 64; use two projections and onellm_swiglu");
     ONELLM_REQUIRE(K % 16 == 0 && I % 8 == 0, ONELLM_ERR_UNSUPPORTED, "gemm_swiglu: need K %% 16 == 0, I %% 8 == 0");
     ONELLM_REQUIRE(aligned16(x) && aligned16(Wg) && aligned16(Wu) && aligned16(out), ONELLM_ERR_ARG,
                    "gemm_swiglu: pointers must be 16-byte aligned");

@@ -1,0 +1,87 @@
+"""Runs one hot kernel alone on a fixed, small case: the target of `ncu` captures.
+
+    python -m onellm_b200.kernel_cases gate_up|down|qkv|o_proj|lm_head|attn|norm [--iters N] [--batch B] [--ctx C]
+
+Each case holds a few hundred MB on the device (more than the 126 MB L2, far less than a
+full model) and launches the kernel `--iters` times on rotating buffers; it prints the mean
+time per launch from CUDA events and the algorithmic GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+import onellm_b200 as ob
+
+H_, D_, HID, INTER, VOCAB = 32, 128, 4096, 11008, 32000
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm"])
+    ap.add_argument("--iters", type=int, default=6)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=2040)
+    a = ap.parse_args()
+    B = a.batch
+    torch.cuda.set_device(0)
+    torch.manual_seed(0)
+    st = torch.cuda.current_stream()
+    rnd = lambda *s: (0.02 * torch.randn(*s, device="cuda")).half()
+    rot = 3
+    if a.case == "gate_up":
+        x, wg, wu = torch.randn(B, HID, device="cuda").half(), [rnd(HID, INTER) for _ in range(rot)], [rnd(HID, INTER) for _ in range(rot)]
+        out = torch.empty(B, INTER, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.gemm_swiglu(ob.F16, x, wg[i], wu[i], out, B, INTER, HID)
+        nbytes = 2 * HID * INTER * 2 + B * HID * 2 + B * INTER * 2
+    elif a.case in ("down", "qkv", "o_proj"):
+        K, N = {"down": (INTER, HID), "qkv": (HID, 3 * HID), "o_proj": (HID, HID)}[a.case]
+        rot = 5 if a.case == "o_proj" else 3
+        x, w = torch.randn(B, K, device="cuda").half(), [rnd(K, N) for _ in range(rot)]
+        out = torch.empty(B, N, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.gemm(ob.F16, x, w[i], out, B, N, K, ob.W_KN)
+        nbytes = K * N * 2 + B * K * 2 + B * N * 2
+    elif a.case == "lm_head":
+        x, w = torch.randn(B, HID, device="cuda").half(), [rnd(VOCAB, HID) for _ in range(2)]
+        rot = 2
+        out = torch.empty(B, VOCAB, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.gemm(ob.F16, x, w[i], out, B, VOCAB, HID, ob.W_NK)
+        nbytes = VOCAB * HID * 2 + B * HID * 2 + B * VOCAB * 2
+    elif a.case == "attn":
+        S = a.ctx + 8
+        rot = max(2, int(300e6 // (2 * B * H_ * S * D_ * 2)) + 1)
+        kc = [torch.randn(B, H_, S, D_, device="cuda", dtype=torch.float16) for _ in range(rot)]
+        vc = [torch.randn(B, H_, S, D_, device="cuda", dtype=torch.float16) for _ in range(rot)]
+        qkv = torch.randn(B, 3 * H_, D_, device="cuda", dtype=torch.float16)
+        o = torch.empty(B, H_, D_, device="cuda", dtype=torch.float16)
+        wsb = ob.decode_attn_workspace_bytes(B, H_, D_, S)
+        ws = torch.empty(wsb, device="cuda", dtype=torch.uint8)
+        p, step = qkv.data_ptr(), a.ctx + 1
+        fn = lambda i: ob.decode_attn(ob.F16, p, p + H_ * D_ * 2, p + 2 * H_ * D_ * 2, 3 * H_ * D_, 3 * H_ * D_, 3 * H_ * D_,
+                                      None, None, None, kc[i], vc[i], H_ * S * D_, S * D_, D_, B, H_, H_, D_, step, step - 1,
+                                      D_, 10000.0, D_ ** -0.5, o, H_ * D_, ws, wsb)
+        nbytes = 2 * a.ctx * B * H_ * D_ * 2 + 5 * B * H_ * D_ * 2
+    else:
+        T = 4096
+        rot = 4
+        xs = [torch.randn(T, HID, device="cuda").half() for _ in range(rot)]
+        rs = [torch.randn(T, HID, device="cuda").half() for _ in range(rot)]
+        g = torch.ones(HID, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.add_residual_rmsnorm(ob.F16, rs[i], xs[i], None, g, 1e-5, T, HID)
+        nbytes = 4 * T * HID * 2 + HID * 2
+    for i in range(3):
+        fn(i % rot)
+    st.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for i in range(a.iters):
+        fn(i % rot)
+    e1.record(st)
+    st.synchronize()
+    t = e0.elapsed_time(e1) / a.iters * 1e-3
+    print(f"{a.case}: {t * 1e6:.1f} us/launch, {nbytes / t / 1e9:.0f} GB/s algorithmic ({nbytes} bytes)")
+
+
+if __name__ == "__main__":
+    main()
