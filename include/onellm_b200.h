@@ -88,6 +88,34 @@ ONELLM_API int onellm_decode_attn(int dtype, const void* q, const void* k, const
                                   void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * onellm_decode_attn for callers that cannot allocate device memory.
+ * No counterpart in the reference (its layers allocate scratch through BaseAllocator).
+ *
+ * Same arguments and results as onellm_decode_attn, without the workspace: the split-KV partials
+ * go to a fixed 8 MiB array inside the library image (onellm_decode_attn_static_scratch_bytes()),
+ * which every GPU that loads the library holds until the process exits.  Meant for hosts that own
+ * all device memory themselves and must not, or cannot, call cudaMalloc on behalf of a kernel
+ * (a server with a pool pinned at start-up, a plugin inside another framework's allocator).
+ * The call performs no CUDA allocation or free of any kind.
+ *
+ * Limits: a shape is accepted only if its worst case, onellm_decode_attn_workspace_bytes(B, H, D,
+ * step), fits the array; otherwise the call fails with ONELLM_ERR_WORKSPACE and a message naming
+ * both sizes.  Llama-2-7B decode at batch 8 and 2048 rows needs 4.3 MiB by that bound.
+ * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+ * that device current): make that call before any stream capture.  All calls share the array:
+ * calls that overlap on the GPU (other streams or host threads) race and must be serialised.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API size_t onellm_decode_attn_static_scratch_bytes(void);
+
+ONELLM_API int onellm_decode_attn_static(int dtype, const void* q, const void* k, const void* v,
+                                         long q_stride_b, long k_stride_b, long v_stride_b,
+                                         const void* bias_q, const void* bias_k, const void* bias_v,
+                                         void* k_cache, void* v_cache, long cs_b, long cs_h, long cs_s,
+                                         int B, int H, int Hkv, int D, int step, const int* step_dev,
+                                         int rope_pos, int rot_dim, float rope_base, float scale,
+                                         void* out, long out_stride_b, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * RMSNorm in place: x <- gamma * x * rsqrt(mean(x^2) + eps), x [num_tokens, hidden].
  * Replaces launchRMSNorm (src/kernels/rmsnorm_kernel.h:6-9, rmsnorm_kernel.cu:47-103).
  * gamma has the dtype of x.  hidden*sizeof(T) must be a multiple of 16.

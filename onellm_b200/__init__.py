@@ -46,6 +46,7 @@ def lib() -> C.CDLL:
         l = C.CDLL(LIB_PATH)
         l.onellm_last_error.restype = C.c_char_p
         l.onellm_decode_attn_workspace_bytes.restype = C.c_size_t
+        l.onellm_decode_attn_static_scratch_bytes.restype = C.c_size_t
         l.onellm_llama_device_bytes.restype = C.c_size_t
         l.onellm_llama_stream.restype = C.c_void_p
         l.onellm_llama_destroy.restype = None
@@ -87,6 +88,19 @@ def decode_attn(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias
         C.c_long(cs_s), C.c_int(B), C.c_int(H), C.c_int(Hkv), C.c_int(D), C.c_int(step), _p(step_dev),
         C.c_int(rope_pos), C.c_int(rot_dim), C.c_float(rope_base), C.c_float(scale), _p(out),
         C.c_long(out_stride_b), _p(workspace), C.c_size_t(workspace_bytes), _stream(stream)))
+
+
+def decode_attn_static(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache,
+                       cs_b, cs_h, cs_s, B, H, Hkv, D, step, rope_pos, rot_dim, rope_base, scale, out, out_stride_b,
+                       step_dev=None, stream=None):
+    """decode_attn with the split-KV scratch taken from the library's built-in array: for hosts that
+    cannot allocate device memory.  Calls sharing the GPU must not overlap (one shared array)."""
+    _check(lib().onellm_decode_attn_static(
+        C.c_int(dtype), _p(q), _p(k), _p(v), C.c_long(q_stride_b), C.c_long(k_stride_b), C.c_long(v_stride_b),
+        _p(bias_q), _p(bias_k), _p(bias_v), _p(k_cache), _p(v_cache), C.c_long(cs_b), C.c_long(cs_h),
+        C.c_long(cs_s), C.c_int(B), C.c_int(H), C.c_int(Hkv), C.c_int(D), C.c_int(step), _p(step_dev),
+        C.c_int(rope_pos), C.c_int(rot_dim), C.c_float(rope_base), C.c_float(scale), _p(out),
+        C.c_long(out_stride_b), _stream(stream)))
 
 
 def rmsnorm(dtype, x, gamma, eps, num_tokens, hidden, stream=None):

@@ -578,3 +578,71 @@ extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const
     ONELLM_CHECK_LAUNCH();
     return ONELLM_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Some hosts of this library hand every byte of device memory out themselves and are not able
+// to call cudaMalloc for a kernel's scratch: a serving process whose memory pool was sized and
+// pinned at start-up, a plugin running inside another framework's allocator, code running where
+// the CUDA allocator must not be re-entered.  For them the split-KV partials of the attention
+// kernel live in a fixed array inside the library image instead of a caller-provided workspace.
+// Every GPU that loads the library holds these kStaticScratchBytes until the process exits.
+//
+// In host code `g_attn_scratch` is only a handle for the symbol, not a device address: passing it
+// to a kernel would fault or silently use the wrong memory.  Its device address is looked up once
+// per device with cudaGetSymbolAddress, with that device current, on the first call made on that
+// device; that first call should therefore happen before any stream capture.
+//
+// All calls share the one array and it keeps the previous call's contents.  Nothing in it has to
+// start at zero (every partial that is read was written by the same launch), but two calls that
+// overlap on the GPU (different streams, or different host threads) race on it: serialise them.
+// ---------------------------------------------------------------------------------------------
+namespace onellm {
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_attn_scratch[kStaticScratchBytes];
+
+// device address of g_attn_scratch on the current device (looked up once per device)
+static int static_scratch(void** out)
+{
+    constexpr int kMaxDevices = 64;
+    static void* addr[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = 0;
+    ONELLM_CUDA(cudaGetDevice(&dev));
+    ONELLM_REQUIRE(dev >= 0 && dev < kMaxDevices, ONELLM_ERR_UNSUPPORTED, "decode_attn_static: device index %d", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void* p = nullptr;
+        ONELLM_CUDA(cudaGetSymbolAddress(&p, g_attn_scratch));
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return ONELLM_OK;
+}
+}  // namespace onellm
+
+extern "C" size_t onellm_decode_attn_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int onellm_decode_attn_static(int dtype, const void* q, const void* k, const void* v, long q_stride_b,
+                                         long k_stride_b, long v_stride_b, const void* bias_q, const void* bias_k,
+                                         const void* bias_v, void* k_cache, void* v_cache, long cs_b, long cs_h,
+                                         long cs_s, int B, int H, int Hkv, int D, int step, const int* step_dev,
+                                         int rope_pos, int rot_dim, float rope_base, float scale, void* out,
+                                         long out_stride_b, void* stream)
+{
+    // The bound is the documented worst case for the shape, not what this launch happens to use,
+    // so that a shape is either always accepted or always refused.
+    const size_t bound = onellm_decode_attn_workspace_bytes(B, H, D, step);
+    ONELLM_REQUIRE(bound != 0 && bound <= kStaticScratchBytes, ONELLM_ERR_WORKSPACE,
+                   "decode_attn_static: B=%d H=%d D=%d step=%d may need %zu bytes of split-KV scratch, the array "
+                   "built into the library holds %zu; use onellm_decode_attn with a caller workspace",
+                   B, H, D, step, bound, kStaticScratchBytes);
+    void* scratch = nullptr;
+    const int rc0 = static_scratch(&scratch);
+    if (rc0) return rc0;
+    const int rc = onellm_decode_attn(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache,
+                                      v_cache, cs_b, cs_h, cs_s, B, H, Hkv, D, step, step_dev, rope_pos, rot_dim,
+                                      rope_base, scale, out, out_stride_b, scratch, kStaticScratchBytes, stream);
+    return rc;
+}
