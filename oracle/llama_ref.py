@@ -108,3 +108,69 @@ class LlamaRef:
     @staticmethod
     def greedy(logits):
         return topk(logits, 1)[1][:, 0]
+
+
+def tp_slice(w, cfg, rank, size):
+    """The tensor-parallel slice rank `rank` of `size` keeps: query/KV heads and FFN columns, with the
+    matching rows of wo / w2 (the scheme of SURVEY 8e; what the engine's loader cuts from the files)."""
+    H, Hkv, D, I = cfg["head_num"], cfg["kv_head_num"], cfg["head_size"], cfg["inter_size"]
+    Hl, Hkvl, Il = H // size, Hkv // size, I // size
+    qs = slice(rank * Hl * D, (rank + 1) * Hl * D)
+    ks = slice(H * D + rank * Hkvl * D, H * D + (rank + 1) * Hkvl * D)
+    vs = slice((H + Hkv) * D + rank * Hkvl * D, (H + Hkv) * D + (rank + 1) * Hkvl * D)
+    out = {"norm": w["norm"], "tok_embeddings": w["tok_embeddings"], "output": w["output"], "layers": []}
+    for lw in w["layers"]:
+        s = {"attention_norm": lw["attention_norm"], "ffn_norm": lw["ffn_norm"],
+             "w_qkv": np.concatenate([lw["w_qkv"][:, qs], lw["w_qkv"][:, ks], lw["w_qkv"][:, vs]], axis=1),
+             "wo": lw["wo"][rank * Hl * D:(rank + 1) * Hl * D], "w1": lw["w1"][:, rank * Il:(rank + 1) * Il],
+             "w3": lw["w3"][:, rank * Il:(rank + 1) * Il], "w2": lw["w2"][rank * Il:(rank + 1) * Il]}
+        if "b_qkv" in lw:
+            s["b_qkv"] = np.concatenate([lw["b_qkv"][qs], lw["b_qkv"][ks], lw["b_qkv"][vs]])
+            s["b_o"] = lw["b_o"]
+        out["layers"].append({k: np.ascontiguousarray(v) for k, v in s.items()})
+    return out
+
+
+class LlamaRefTP(LlamaRef):
+    """One tensor-parallel rank: local heads and FFN columns, `allreduce(array)` sums the partial
+    o_proj / down_proj outputs over the ranks (any backend; the CPU tests use gloo)."""
+
+    def __init__(self, cfg, weights, batch, rank, size, allreduce, storage="f16"):
+        local = dict(cfg, head_num=cfg["head_num"] // size, kv_head_num=cfg["kv_head_num"] // size,
+                     inter_size=cfg["inter_size"] // size)
+        super().__init__(local, tp_slice(weights, cfg, rank, size), batch, storage)
+        self.full_hidden = cfg["hidden"]
+        self.allreduce = allreduce
+
+    def step(self, ids, lm_head=True, layers=None):
+        c, w, r = self.cfg, self.w, self.rnd
+        H, Hkv, D = c["head_num"], c["kv_head_num"], c["head_size"]
+        eps = c.get("rms_eps", 1e-5)
+        step = self.cur_len + 1
+        res = embedding(np.asarray(ids, np.int32), w["tok_embeddings"])
+        y = r(rmsnorm(res, w["layers"][0]["attention_norm"], eps))
+        for l in range(c["num_layers"]):
+            lw = w["layers"][l]
+            qkv = r(gemm(y, lw["w_qkv"])).reshape(self.B, H + 2 * Hkv, D)
+            b = lw.get("b_qkv")
+            bq = None if b is None else b[:H * D]
+            bk = None if b is None else b[H * D:(H + Hkv) * D]
+            bv = None if b is None else b[(H + Hkv) * D:]
+            kc, vc = self.k_cache[l], self.v_cache[l]
+            attn = decode_attn(qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:], kc, vc, step, rope_pos=step - 1,
+                               rot_dim=c.get("rot_dim", D) or D, rope_base=c.get("rope_base", 10000.0), bias_q=bq,
+                               bias_k=bk, bias_v=bv)
+            kc[:, :, step - 1], vc[:, :, step - 1] = r(kc[:, :, step - 1]), r(vc[:, :, step - 1])
+            o = r(self.allreduce(r(gemm(r(attn).reshape(self.B, H * D), lw["wo"]))))
+            y, res = add_residual_rmsnorm(res, o, lw.get("b_o"), lw["ffn_norm"], eps)
+            y, res = r(y), r(res)
+            act = r(swiglu2(gemm(y, lw["w1"]), gemm(y, lw["w3"])))
+            d = r(self.allreduce(r(gemm(act, lw["w2"]))))
+            gamma = w["layers"][l + 1]["attention_norm"] if l + 1 < c["num_layers"] else w["norm"]
+            y, res = add_residual_rmsnorm(res, d, None, gamma, eps)
+            y, res = r(y), r(res)
+        self.cur_len += 1
+        if lm_head:
+            self.logits = r(gemm(y, w["output"], w_is_nk=True))
+            return self.logits
+        return None
