@@ -192,7 +192,7 @@ def kernel_rooflines(ob, torch, model, batch, ctx, hbm_peak):
     out = torch.empty(batch, I, device="cuda", dtype=torch.float16)
     t = timeit(lambda i: ob.gemm_swiglu(ob.F16, x, wg[i], wu[i], out, batch, I, h), n_rot)
     bytes_ = 2 * h * I * 2 + batch * h * 2 + batch * I * 2
-    res["gate_up_swiglu"] = {"kernel": "skinny_kn_kernel<1,true,2>", "bytes": bytes_, "us": t * 1e6,
+    res["gate_up_swiglu"] = {"kernel": "skinny_kn_staged_kernel<1,true>", "bytes": bytes_, "us": t * 1e6,
                              "gbs": bytes_ / t / 1e9, "frac": bytes_ / t / 1e9 / hbm_peak}
     del wg, wu
     # down projection
@@ -201,7 +201,7 @@ def kernel_rooflines(ob, torch, model, batch, ctx, hbm_peak):
     y = torch.empty(batch, h, device="cuda", dtype=torch.float16)
     t = timeit(lambda i: ob.gemm(ob.F16, a, wd[i], y, batch, h, I), n_rot)
     bytes_ = h * I * 2 + batch * I * 2 + batch * h * 2
-    res["down_proj"] = {"kernel": "skinny_kn_kernel<1,false,4>", "bytes": bytes_, "us": t * 1e6,
+    res["down_proj"] = {"kernel": "skinny_kn_staged_kernel<1,false>", "bytes": bytes_, "us": t * 1e6,
                         "gbs": bytes_ / t / 1e9, "frac": bytes_ / t / 1e9 / hbm_peak}
     del wd
     # decode attention at the given context: one layer's K and V are 2 x B*H*ctx*D*2 bytes
