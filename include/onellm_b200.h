@@ -153,6 +153,19 @@ ONELLM_API int onellm_gemm(int dtype, const void* x, const void* W, void* y, int
 ONELLM_API int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, const void* Wu, void* out,
                                   int M, int I, int K, void* stream);
 
+/* Fused add-bias-residual RMSNorm in front of a projection (fp16, M <= 16, [K,N] weights):
+ *     r = x + residual (+ bias);   residual_out = r;
+ *     xn = gamma * r * rsqrt(mean(r^2) + eps);   y = xn . W      (Wu == NULL)
+ *                                                y = silu(xn . W) * (xn . Wu)
+ * x == NULL: r = residual (a plain RMSNorm in front of the projection; residual_out is ignored).
+ * residual_out must not alias residual.  One launch replaces launchFusedAddBiasResidualRMSNorm
+ * followed by launchLinearGemm(s) (and launchAct), the order of
+ * src/layers/decoder/self_decoder.cpp:50-62 and src/layers/ffn/ffn.cpp:62-66. */
+ONELLM_API int onellm_add_residual_rmsnorm_gemm(int dtype, const void* x, const void* residual, const void* bias,
+                                                const void* gamma, float eps, void* residual_out,
+                                                const void* W, const void* Wu, void* y, int M, int N, int K,
+                                                void* stream);
+
 /* Standalone SwiGLU on input [tokens, 2, I] -> out [tokens, I].
  * Replaces launchAct<T> (src/kernels/activation_kernel.h:2-3, activation_kernel.cu:10-32). */
 ONELLM_API int onellm_swiglu(int dtype, const void* input, void* out, int tokens, int inter,

@@ -124,6 +124,12 @@ def gemm_swiglu(dtype, x, Wg, Wu, out, M, I, K, stream=None):
                                     C.c_int(K), _stream(stream)))
 
 
+def add_residual_rmsnorm_gemm(dtype, x, residual, bias, gamma, eps, residual_out, W, Wu, y, M, N, K, stream=None):
+    _check(lib().onellm_add_residual_rmsnorm_gemm(C.c_int(dtype), _p(x), _p(residual), _p(bias), _p(gamma),
+                                                  C.c_float(eps), _p(residual_out), _p(W), _p(Wu), _p(y), C.c_int(M),
+                                                  C.c_int(N), C.c_int(K), _stream(stream)))
+
+
 def swiglu(dtype, inp, out, tokens, inter, stream=None):
     _check(lib().onellm_swiglu(C.c_int(dtype), _p(inp), _p(out), C.c_int(tokens), C.c_int(inter),
                                _stream(stream)))

@@ -357,6 +357,309 @@ __global__ void decode_attn_combine_kernel(const DecodeAttnParams p)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core variant for fp16 caches with D = 64 or 128.
+//
+// Same contract as decode_attn_kernel.  The SIMT kernel above spends ~45 instructions per row
+// and lane group on conversions, FMAs and shuffles and ends up bounded by instruction issue
+// (67 % issue-slot use at 5.2 TB/s); here a warp handles a 16-row tile with 2 * D/8 mma.m16n8k16:
+//   S^T[head, row] = q[head, :] . K[row, :]^T      (A = q from registers, B = K rows via ldmatrix)
+//   O[head, :]    += P[head, row] . V[row, :]      (A = P straight from the S accumulators,
+//                                                   B = V rows via ldmatrix.trans)
+// The up to 8 query heads that share a KV head sit on the M axis (rows 8..15 of every tile are
+// padding), so K and V are read once per group.  Each WARP owns a contiguous range of the
+// block's rows and its own ring of cp.async stages: there is no block-wide barrier in the main
+// loop.  With about two blocks per SM the whole context of a (sequence, KV head) pair fits one
+// block, so large batches need no split and no merge kernel.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi)
+{
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+constexpr int kMmaWarps = 4;
+constexpr int kMmaTileRows = 16;
+
+template <int D, int G>
+__global__ void __launch_bounds__(kMmaWarps * 32) decode_attn_mma_kernel(const DecodeAttnParams p)
+{
+    constexpr int ROWB = D * 2;                       // bytes per K or V row
+    constexpr int CH = D / 8;                         // 16-byte chunks per row
+    constexpr int TILE = 2 * kMmaTileRows * ROWB;     // K rows then V rows of one stage
+    constexpr int KS = D / 16;                        // k-steps of q.K^T, pairs of d tiles of P.V
+    constexpr int EPL = D / 32;                       // elements of a row per lane (new-row path)
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ __align__(16) __half q_s[8][D];
+    __shared__ float sm_m[kMmaWarps][G], sm_l[kMmaWarps][G];
+    // per-warp accumulators for the final merge reuse the ring once the main loop is over
+    float (*sm_acc)[G][D] = reinterpret_cast<float (*)[G][D]>(ring);
+
+    const int split = blockIdx.x;
+    const int h0 = blockIdx.y * G;
+    const int b = blockIdx.z;
+    const int qpk = p.H / p.Hkv;
+    const int hk = h0 / qpk;
+    const bool writes_cache = (h0 % qpk) == 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+    const int step = p.step_dev ? *p.step_dev : p.step;
+    const float pos = (float)(step + p.rope_delta);
+    const int n_cached = step - 1;
+    const int n_split = effective_splits(n_cached, p.chunk);
+    if (split >= n_split) {
+        pdl_launch_dependents();
+        pdl_wait();
+        return;
+    }
+    const bool owns_new = (split == n_split - 1);
+    const int row0 = split * p.chunk;
+    const int row1 = min(row0 + p.chunk, n_cached) + (owns_new ? 1 : 0);  // the new row rides at the end
+    // rows of this warp: contiguous, whole tiles except at the end
+    const int rows_total = row1 - row0;
+    int per_warp = (rows_total + kMmaWarps - 1) / kMmaWarps;
+    per_warp = (per_warp + kMmaTileRows - 1) / kMmaTileRows * kMmaTileRows;
+    const int wr0 = min(row0 + warp * per_warp, row1);
+    const int wr1 = min(wr0 + per_warp, row1);
+    const int n_tiles = (wr1 - wr0 + kMmaTileRows - 1) / kMmaTileRows;
+
+    const __half* kc = reinterpret_cast<const __half*>(p.kc) + b * p.cs_b + hk * p.cs_h;
+    const __half* vc = reinterpret_cast<const __half*>(p.vc) + b * p.cs_b + hk * p.cs_h;
+    const int nst = p.nst;
+    const uint32_t ring_base = (uint32_t)__cvta_generic_to_shared(ring) + (uint32_t)(warp * nst * TILE);
+    unsigned char* ring_gen = ring + (size_t)warp * nst * TILE;
+
+    // this lane's copies of a tile: chunk id = lane + 32*i -> row id/CH, chunk id%CH (a warp-wide
+    // copy covers whole rows); rows at or beyond n_cached are not in the cache yet: zero-filled
+    auto issue = [&](int tile, int buf) {
+        if (tile < n_tiles) {
+            const int r0 = wr0 + tile * kMmaTileRows;
+            const uint32_t sb = ring_base + (uint32_t)(buf * TILE);
+#pragma unroll
+            for (int i = 0; i < (kMmaTileRows * CH) / 32; i++) {
+                const int id = lane + 32 * i;
+                const int row = id / CH, c = id % CH;
+                const int rr = r0 + row;
+                const bool ok = rr < wr1 && rr < n_cached;
+                const long off = ok ? (long)rr * p.cs_s + c * 8 : 0;
+                const uint32_t dst = sb + row * ROWB + ((c ^ (row & 7)) << 4);
+                cp_async16(dst, kc + off, ok ? 16 : 0);
+                cp_async16(dst + kMmaTileRows * ROWB, vc + off, ok ? 16 : 0);
+            }
+        }
+        cp_async_commit();
+    };
+    for (int s = 0; s < nst - 1; s++) issue(s, s);
+
+    // rotation coefficients of the pairs this THREAD rotates when it prepares q (and the new k)
+    // q: thread handles elements (head = threadIdx/ (D/2) ... ) -- see below
+    pdl_wait();
+
+    // q -> bias, RoPE, fp16 into q_s[head][d]; heads >= G are zero
+    for (int idx = threadIdx.x; idx < 8 * (D / 2); idx += kMmaWarps * 32) {
+        const int head = idx / (D / 2), pr = idx % (D / 2);
+        float x = 0.f, y = 0.f;
+        if (head < G) {
+            const __half* qp = reinterpret_cast<const __half*>(p.q) + b * p.q_sb + (long)(h0 + head) * D + 2 * pr;
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(qp));
+            x = v.x;
+            y = v.y;
+            if (p.bq) {
+                const float2 bb = __half22float2(
+                    *reinterpret_cast<const __half2*>(reinterpret_cast<const __half*>(p.bq) + (long)(h0 + head) * D + 2 * pr));
+                x += bb.x;
+                y += bb.y;
+            }
+            if (2 * pr < p.rot_dim) {
+                float sn, cs;
+                sincosf(pos / p.rope_denom[pr], &sn, &cs);
+                const float xr = cs * x - sn * y, yr = cs * y + sn * x;
+                x = xr;
+                y = yr;
+            }
+        }
+        *reinterpret_cast<__half2*>(&q_s[head][2 * pr]) = __floats2half2_rn(x, y);
+    }
+    __syncthreads();
+    uint32_t qa[KS][2];  // A fragments of q: (head g, d 16ks+2t..) and (head g, d 16ks+8+2t..)
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        qa[ks][0] = *reinterpret_cast<const uint32_t*>(&q_s[g][16 * ks + 2 * t]);
+        qa[ks][1] = *reinterpret_cast<const uint32_t*>(&q_s[g][16 * ks + 8 + 2 * t]);
+    }
+
+    float O[2 * KS][2];  // (head g, d 8j+2t, 8j+2t+1); the accumulator halves of heads 8..15 are dropped
+#pragma unroll
+    for (int j = 0; j < 2 * KS; j++) O[j][0] = O[j][1] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's share of the row sum
+
+    // ldmatrix lane addressing inside a tile (K part): matrix mi = lane/8
+    const int mi = lane >> 3, lr = lane & 7;
+    const int k_row = lr + (mi >> 1) * 8, k_chunk = mi & 1;   // S: (rows 0-7 | 8-15) x (chunk 2ks | 2ks+1)
+    const int v_row = lr + (mi & 1) * 8, v_chunk = mi >> 1;   // PV: (rows 0-7 | 8-15) x (chunk 2jp | 2jp+1)
+
+    int buf = 0, fill = nst - 1;
+    for (int tile = 0; tile < n_tiles; tile++) {
+        cp_async_wait_dyn(nst - 2);
+        __syncwarp();
+        const int r0 = wr0 + tile * kMmaTileRows;
+        const uint32_t sb = ring_base + (uint32_t)(buf * TILE);
+        // the new token's row, if it lies in this tile: bias, RoPE, round, store to the tile and the cache
+        if (owns_new && n_cached >= r0 && n_cached < r0 + kMmaTileRows && n_cached < wr1) {
+            const int row = n_cached - r0, d0 = lane * EPL;
+            float kf[EPL], vf[EPL];
+#pragma unroll
+            for (int e = 0; e < EPL; e++) {
+                kf[e] = __half2float(reinterpret_cast<const __half*>(p.k)[b * p.k_sb + (long)hk * D + d0 + e]);
+                vf[e] = __half2float(reinterpret_cast<const __half*>(p.v)[b * p.v_sb + (long)hk * D + d0 + e]);
+                if (p.bk) kf[e] += __half2float(reinterpret_cast<const __half*>(p.bk)[(long)hk * D + d0 + e]);
+                if (p.bv) vf[e] += __half2float(reinterpret_cast<const __half*>(p.bv)[(long)hk * D + d0 + e]);
+            }
+#pragma unroll
+            for (int e = 0; e < EPL; e += 2) {
+                if (d0 + e < p.rot_dim) {
+                    float sn, cs;
+                    sincosf(pos / p.rope_denom[(d0 + e) >> 1], &sn, &cs);
+                    const float x = kf[e], y = kf[e + 1];
+                    kf[e] = cs * x - sn * y;
+                    kf[e + 1] = cs * y + sn * x;
+                }
+            }
+            unsigned char* krow = ring_gen + (size_t)buf * TILE + row * ROWB + ((((d0 >> 3) ^ (row & 7))) << 4) + (d0 & 7) * 2;
+            unsigned char* vrow = krow + kMmaTileRows * ROWB;
+            __half* kd = reinterpret_cast<__half*>(p.kc) + b * p.cs_b + hk * p.cs_h + (long)n_cached * p.cs_s + d0;
+            __half* vd = reinterpret_cast<__half*>(p.vc) + b * p.cs_b + hk * p.cs_h + (long)n_cached * p.cs_s + d0;
+#pragma unroll
+            for (int e = 0; e < EPL; e += 2) {
+                const __half2 kh = __floats2half2_rn(kf[e], kf[e + 1]), vh = __floats2half2_rn(vf[e], vf[e + 1]);
+                *reinterpret_cast<__half2*>(krow + e * 2) = kh;
+                *reinterpret_cast<__half2*>(vrow + e * 2) = vh;
+                if (writes_cache) {
+                    *reinterpret_cast<__half2*>(kd + e) = kh;
+                    *reinterpret_cast<__half2*>(vd + e) = vh;
+                }
+            }
+            __syncwarp();
+        }
+        issue(tile + nst - 1, fill);
+        buf = buf + 1 == nst ? 0 : buf + 1;
+        fill = fill + 1 == nst ? 0 : fill + 1;
+
+        // S^T = q . K^T for the 16 rows of the tile: s0 = rows 0-7, s1 = rows 8-15
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            uint32_t kb[4];
+            const int c = 2 * ks + k_chunk;
+            ldsm_x4(kb, sb + k_row * ROWB + ((c ^ (k_row & 7)) << 4));
+            mma_f16(s0, qa[ks][0], 0u, qa[ks][1], 0u, kb[0], kb[1]);
+            mma_f16(s1, qa[ks][0], 0u, qa[ks][1], 0u, kb[2], kb[3]);
+        }
+        // scale, mask rows beyond the range, running softmax for head g (log2 domain)
+        const int valid = wr1 - r0;  // rows of this tile that exist
+        float sc[4];
+        sc[0] = (2 * t < valid) ? s0[0] * p.scale_log2e : -INFINITY;
+        sc[1] = (2 * t + 1 < valid) ? s0[1] * p.scale_log2e : -INFINITY;
+        sc[2] = (8 + 2 * t < valid) ? s1[0] * p.scale_log2e : -INFINITY;
+        sc[3] = (9 + 2 * t < valid) ? s1[1] * p.scale_log2e : -INFINITY;
+        float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float ms = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = fast_exp2(m_run - ms);
+        m_run = m_new;
+        float pr[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) pr[e] = fast_exp2(sc[e] - ms);
+        l_run = l_run * corr + (pr[0] + pr[1] + pr[2] + pr[3]);
+        const uint32_t pa0 = pack_h2(pr[0], pr[1]), pa2 = pack_h2(pr[2], pr[3]);
+#pragma unroll
+        for (int j = 0; j < 2 * KS; j++) {
+            O[j][0] *= corr;
+            O[j][1] *= corr;
+        }
+        // O += P . V
+#pragma unroll
+        for (int jp = 0; jp < KS; jp++) {
+            uint32_t vb[4];
+            const int c = 2 * jp + v_chunk;
+            ldsm_x4_t(vb, sb + (kMmaTileRows + v_row) * ROWB + ((c ^ (v_row & 7)) << 4));
+            float o0[4] = {O[2 * jp][0], O[2 * jp][1], 0.f, 0.f}, o1[4] = {O[2 * jp + 1][0], O[2 * jp + 1][1], 0.f, 0.f};
+            mma_f16(o0, pa0, 0u, pa2, 0u, vb[0], vb[1]);
+            mma_f16(o1, pa0, 0u, pa2, 0u, vb[2], vb[3]);
+            O[2 * jp][0] = o0[0];
+            O[2 * jp][1] = o0[1];
+            O[2 * jp + 1][0] = o1[0];
+            O[2 * jp + 1][1] = o1[1];
+        }
+    }
+    cp_async_wait<0>();
+    pdl_launch_dependents();
+    __syncthreads();  // every warp is done with its ring before the ring is reused below
+
+    // per-warp results -> shared memory, then the same merge as the SIMT kernel
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (g < G) {
+#pragma unroll
+        for (int j = 0; j < 2 * KS; j++) {
+            sm_acc[warp][g][8 * j + 2 * t] = O[j][0];
+            sm_acc[warp][g][8 * j + 2 * t + 1] = O[j][1];
+        }
+        if (t == 0) {
+            sm_m[warp][g] = m_run;
+            sm_l[warp][g] = l_run;
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += kMmaWarps * 32) {
+        const int gg = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kMmaWarps; i++) M = fmaxf(M, sm_m[i][gg]);
+        float L = 0.f, Ov = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMmaWarps; i++) {
+            const float w = fast_exp2(sm_m[i][gg] - M);  // warps without rows: exp2(-inf) = 0
+            L = fmaf(sm_l[i][gg], w, L);
+            Ov = fmaf(sm_acc[i][gg][d], w, Ov);
+        }
+        const int h = h0 + gg;
+        if (n_split == 1) {
+            reinterpret_cast<__half*>(p.out)[b * p.out_sb + (long)h * D + d] = __float2half_rn(Ov / L);
+        } else {
+            const long base = ((long)b * p.H + h) * p.n_split + split;
+            p.part_acc[base * D + d] = Ov;
+            if (d == 0) {
+                p.part_ml[base * 2] = M;
+                p.part_ml[base * 2 + 1] = L;
+            }
+        }
+    }
+}
+
 constexpr int kMaxSplits = 32;
 
 // Upper bound on the splits any plan uses for `step` rows.
@@ -424,6 +727,49 @@ static AttnPlan plan_attention(int B, int n_head_blocks, int step, int regs_per_
                 best_t = t;
                 best = {ns, c, nst, (size_t)nst * kAttnStageBytes};
             }
+        }
+    }
+    return best;
+}
+
+// Plan for the tensor-core kernel: blocks per SM r in {3, 2, 1} fix the ring depth shared memory
+// allows (2, 3, 6 stages per warp at D = 128); the splits fill r * SMs block slots; the choice is
+// the one with the most bytes in flight among those that need a single wave.
+static AttnPlan plan_attention_mma(int B, int n_head_blocks, int step, int D, int regs_per_sm)
+{
+    const int n_cached = step > 1 ? step - 1 : 0;
+    const long base = (long)B * n_head_blocks;
+    const int ms = max_splits(step);
+    const int sms = num_sms();
+    const size_t tile = (size_t)2 * kMmaTileRows * D * 2;
+    // fallback (never taken while any ring fits): one split over all rows, two stages
+    AttnPlan best = {1, (n_cached + 63) / 64 * 64 < kMinChunkRows ? kMinChunkRows : (n_cached + 63) / 64 * 64, 2,
+                     2 * kMmaWarps * tile};
+    double best_score = -1.0e300;  // scores may be negative (the merge penalty)
+    for (int r = regs_per_sm < 3 ? regs_per_sm : 3; r >= 1; r--) {
+        const size_t budget = (size_t)(227 * 1024) / r - 4096;
+        int nst = (int)(budget / (kMmaWarps * tile));
+        if (nst > 8) nst = 8;
+        if (nst < 2) continue;
+        const long slots = (long)r * sms;
+        long n = slots / base;
+        if (n < 1) n = 1;
+        if (n > ms) n = ms;
+        int c = (int)((n_cached + n - 1) / n);
+        c = (c + 63) / 64 * 64;  // whole tiles for each of the four warps
+        if (c < kMinChunkRows) c = kMinChunkRows;
+        int ns = (n_cached + c - 1) / c;
+        if (ns < 1) ns = 1;
+        const long total = base * ns;
+        const long waves = (total + slots - 1) / slots;
+        const long resident = total < slots ? total : slots;
+        const int tiles_per_warp = (c / kMmaWarps + kMmaTileRows - 1) / kMmaTileRows;
+        const int depth = nst - 1 < tiles_per_warp ? nst - 1 : tiles_per_warp;
+        const double inflight = (double)resident * kMmaWarps * depth * (double)tile;
+        const double score = inflight / (double)waves - (ns > 1 ? 1.0e6 : 0.0);  // a merge kernel costs a little
+        if (score > best_score) {
+            best_score = score;
+            best = {ns, c, nst, (size_t)nst * kMmaWarps * tile};
         }
     }
     return best;
@@ -549,12 +895,29 @@ extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const
 
     const int G = pick_group(H / Hkv);
     const int lpr = (int)(row_bytes / 16);
-    const AttnKernel kern = dtype == ONELLM_F16 ? attn_kernel_for<__half>(lpr, G) : attn_kernel_for<float>(lpr, G);
-    const AttnKernelInfo info = kernel_info(kern);
-    const AttnPlan plan = plan_attention(B, H / G, step, info.blocks_per_sm_regs, info.static_smem, row_bytes);
+    const bool use_mma = dtype == ONELLM_F16 && (D == 64 || D == 128);
+    AttnKernel kern;
+    AttnPlan plan;
+    if (use_mma) {
+        kern = D == 128 ? (G == 8 ? decode_attn_mma_kernel<128, 8> : G == 4 ? decode_attn_mma_kernel<128, 4>
+                                   : G == 2 ? decode_attn_mma_kernel<128, 2> : decode_attn_mma_kernel<128, 1>)
+                        : (G == 8 ? decode_attn_mma_kernel<64, 8> : G == 4 ? decode_attn_mma_kernel<64, 4>
+                                   : G == 2 ? decode_attn_mma_kernel<64, 2> : decode_attn_mma_kernel<64, 1>);
+        const AttnKernelInfo info = kernel_info(kern);  // also raises the dynamic shared-memory limit once
+        plan = plan_attention_mma(B, H / G, step, D, info.blocks_per_sm_regs);
+    } else {
+        kern = dtype == ONELLM_F16 ? attn_kernel_for<__half>(lpr, G) : attn_kernel_for<float>(lpr, G);
+        const AttnKernelInfo info = kernel_info(kern);
+        plan = plan_attention(B, H / G, step, info.blocks_per_sm_regs, info.static_smem, row_bytes);
+    }
     p.n_split = plan.n_split;
     p.chunk = plan.chunk;
     p.nst = plan.nst;
+    // the kernels derive their split count from `chunk`: it must cover every cached row within the
+    // launched grid, or a block would take itself for a partial and write to a missing workspace
+    ONELLM_REQUIRE((long)plan.chunk * plan.n_split >= step - 1 && plan.nst >= 2, ONELLM_ERR_UNSUPPORTED,
+                   "decode_attn: internal plan does not cover the rows (chunk=%d splits=%d step=%d)", plan.chunk,
+                   plan.n_split, step);
     p.part_acc = nullptr;
     p.part_ml = nullptr;
     if (p.n_split > 1) {

@@ -36,6 +36,7 @@
 #include <nccl.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
 #include <string>
 #include <vector>
@@ -268,41 +269,42 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         gather_prompt_ids_kernel<<<(B + 127) / 128, 128, 0, st>>>(m.d_prompt, prompt_len, m.d_step, m.d_ids, B);
         m.launches++;
     }
-    RC(embedding_launch(ONELLM_F16, m.d_ids, m.y, m.res, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
-    RC(onellm_rmsnorm(ONELLM_F16, m.y, m.layers[0].attn_norm, c.rms_eps, B, h, sp));
-    m.launches += 3;
     const long cs_b = (long)m.Hkvl * c.max_seq_len * D, cs_h = (long)c.max_seq_len * D, cs_s = D;
     const float scale = 1.0f / sqrtf((float)D);
-    for (int l = 0; l < c.num_layers; l++) {
+    auto attention = [&](int l) -> int {
         const LayerW& L = m.layers[l];
-        RC(onellm_gemm(ONELLM_F16, m.y, L.w_qkv, m.qkv, B, m.qkv_cols, h, ONELLM_W_KN, sp));
         const __half* q = m.qkv;
         const __half* k = m.qkv + (size_t)m.Hl * D;
         const __half* v = m.qkv + (size_t)(m.Hl + m.Hkvl) * D;
         const __half* bq = L.b_qkv;
         const __half* bk = L.b_qkv ? L.b_qkv + (size_t)m.Hl * D : nullptr;
         const __half* bv = L.b_qkv ? L.b_qkv + (size_t)(m.Hl + m.Hkvl) * D : nullptr;
-        RC(onellm_decode_attn(ONELLM_F16, q, k, v, m.qkv_cols, m.qkv_cols, m.qkv_cols, bq, bk, bv,
-                              m.k_cache + (size_t)l * m.cache_layer_elems, m.v_cache + (size_t)l * m.cache_layer_elems,
-                              cs_b, cs_h, cs_s, B, m.Hl, m.Hkvl, D, step_bound, m.d_step, step_bound - 1, c.rot_dim,
-                              c.rope_base, scale, m.attn, (long)m.Hl * D, m.attn_ws, m.attn_ws_bytes, sp));
-        RC(onellm_gemm(ONELLM_F16, m.attn, L.wo, m.y, B, h, m.Hl * D, ONELLM_W_KN, sp));
-        RC(tp_allreduce(m, m.y, (size_t)B * h));
-        RC(onellm_add_residual_rmsnorm(ONELLM_F16, m.res, m.y, L.b_o, L.ffn_norm, c.rms_eps, B, h, sp));
-        if (B <= 32) {
+        return onellm_decode_attn(ONELLM_F16, q, k, v, m.qkv_cols, m.qkv_cols, m.qkv_cols, bq, bk, bv,
+                                  m.k_cache + (size_t)l * m.cache_layer_elems, m.v_cache + (size_t)l * m.cache_layer_elems,
+                                  cs_b, cs_h, cs_s, B, m.Hl, m.Hkvl, D, step_bound, m.d_step, step_bound - 1, c.rot_dim,
+                                  c.rope_base, scale, m.attn, (long)m.Hl * D, m.attn_ws, m.attn_ws_bytes, sp);
+    };
+    {
+        // (onellm_add_residual_rmsnorm_gemm folds each norm into the projection after it; measured on
+        // B200 it is no faster than the two launches below, because every block of the projection
+        // repeats the row statistics, so the model keeps the separate norm kernels)
+        RC(embedding_launch(ONELLM_F16, m.d_ids, m.y, m.res, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
+        RC(onellm_rmsnorm(ONELLM_F16, m.y, m.layers[0].attn_norm, c.rms_eps, B, h, sp));
+        m.launches += 3;
+        for (int l = 0; l < c.num_layers; l++) {
+            const LayerW& L = m.layers[l];
+            RC(onellm_gemm(ONELLM_F16, m.y, L.w_qkv, m.qkv, B, m.qkv_cols, h, ONELLM_W_KN, sp));
+            RC(attention(l));
+            RC(onellm_gemm(ONELLM_F16, m.attn, L.wo, m.y, B, h, m.Hl * D, ONELLM_W_KN, sp));
+            RC(tp_allreduce(m, m.y, (size_t)B * h));
+            RC(onellm_add_residual_rmsnorm(ONELLM_F16, m.res, m.y, L.b_o, L.ffn_norm, c.rms_eps, B, h, sp));
             RC(onellm_gemm_swiglu(ONELLM_F16, m.y, L.w1, L.w3, m.act, B, m.Il, h, sp));
-            m.launches += 1;
-        } else {
-            RC(onellm_gemm(ONELLM_F16, m.y, L.w1, m.act, B, m.Il, h, ONELLM_W_KN, sp));
-            RC(onellm_gemm(ONELLM_F16, m.y, L.w3, m.act2, B, m.Il, h, ONELLM_W_KN, sp));
-            RC(swiglu_pair_f16(m.act, m.act2, m.act, (size_t)B * m.Il, st));
-            m.launches += 3;
+            RC(onellm_gemm(ONELLM_F16, m.act, L.w2, m.y, B, h, m.Il, ONELLM_W_KN, sp));
+            RC(tp_allreduce(m, m.y, (size_t)B * h));
+            const __half* next_gamma = (l + 1 < c.num_layers) ? m.layers[l + 1].attn_norm : m.out_norm;
+            RC(onellm_add_residual_rmsnorm(ONELLM_F16, m.res, m.y, nullptr, next_gamma, c.rms_eps, B, h, sp));
+            m.launches += 8;  // qkv, attention + combine, o, norm, gate/up, down, norm
         }
-        RC(onellm_gemm(ONELLM_F16, m.act, L.w2, m.y, B, h, m.Il, ONELLM_W_KN, sp));
-        RC(tp_allreduce(m, m.y, (size_t)B * h));
-        const __half* next_gamma = (l + 1 < c.num_layers) ? m.layers[l + 1].attn_norm : m.out_norm;
-        RC(onellm_add_residual_rmsnorm(ONELLM_F16, m.res, m.y, nullptr, next_gamma, c.rms_eps, B, h, sp));
-        m.launches += 7;  // qkv, attention (+ combine counted as one), o, norm, down, norm
     }
     if (mode & MODE_HEAD) {
         RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));

@@ -7,15 +7,18 @@
 // The weight tile of a block is 128 columns wide; it is brought in by 16-byte cp.async copies,
 // 32 rows (8 KB) per stage, through a ring of stages deep enough that the bytes in flight per
 // SM are set by shared memory, not by registers or by how many warps are resident.  Every
-// warp-wide copy instruction covers two whole 256-byte row segments.  The 16-byte chunks of a
+// warp-wide copy instruction covers two whole 256-byte row segments; source pointers are
+// set up once and advance by a constant per stage.  The 16-byte chunks of a
 // row are XOR-swizzled with the row number so that ldmatrix reads them back without bank
 // conflicts; ldmatrix.trans turns the [k][n] tile into the 16x16 "row" operand of
 // mma.m16n8k16 (the WEIGHT is the 16-row operand, the 8 tokens of a batch block the 8-column
-// operand, so a batch of 8 wastes nothing).  The four warps of a block split the 128 columns,
+// operand, so a batch of 8 wastes nothing).  The eight warps of a block split the 128 columns,
 // so no cross-warp reduction is needed; K is split across the blocks of a thread-block
 // cluster and the partial sums meet in distributed shared memory in a fixed order.
 #include <cooperative_groups.h>
 #include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include <algorithm>
 #include <map>
@@ -29,7 +32,7 @@ namespace cg = cooperative_groups;
 
 namespace onellm {
 
-constexpr int kStThreads = 128;
+constexpr int kStThreads = 256;
 constexpr int kBN = 128;                 // columns per block
 constexpr int kKC = 32;                  // rows per stage
 constexpr int kStageBytes = kKC * kBN * 2;  // 8 KB per weight matrix
@@ -53,15 +56,32 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 
 // y[M,N] = x[M,K] . W0                    (DUAL = false)
 // y[M,N] = silu(x.W0) * (x.W1)            (DUAL = true)
-// grid = (ceil(N/128), KS), cluster (1, KS, 1); M <= 8*MB; K % 16 == 0; N % 8 == 0.
-template <int MB, bool DUAL>
+// grid = (ceil(N/128), KS), cluster (1, KS, 1); 256 threads; M <= 8*MB; K % 16 == 0; N % 8 == 0.
+// FUSED: x is not read as is; the block first forms, for its rows of K,
+//     r = x + residual (+ bias),   xn = gamma * r * rsqrt(mean_over_K(r^2) + eps)
+// (the fused add-bias-residual RMSNorm of src/kernels/fused_addresidual_norm.cu:51-107 in front of
+// the projection, as src/layers/decoder/self_decoder.cpp:50-73 sequences them), keeps xn in shared
+// memory for the whole kernel and, in the blocks of column tile 0, stores r as the new residual.
+// `x` may be NULL (r = residual: the plain RMSNorm in front of layer 0).
+struct FusedNormArgs {
+    const __half* residual;  // [M, K]
+    const __half* bias;      // [K] or NULL
+    const __half* gamma;     // [K]
+    __half* residual_out;    // [M, K], must not alias residual (other blocks still read it); NULL when x is NULL
+    float eps;
+};
+
+template <int MB, bool DUAL, bool FUSED>
 __global__ void __launch_bounds__(kStThreads)
 skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__ W0, const __half* __restrict__ W1,
-                        __half* __restrict__ y, int M, int N, int K, int stages_per_block, int nst)
+                        __half* __restrict__ y, int M, int N, int K, int stages_per_block, int nst,
+                        const FusedNormArgs fn)
 {
     constexpr int NW = DUAL ? 2 : 1;
     constexpr int MP = 8 * MB;
-    constexpr int STAGE = NW * kStageBytes + MP * kXRowBytes;  // weights, then the activations of the same rows
+    // a stage holds the weights and (not FUSED) the activations of the same 32 rows
+    constexpr int STAGE = NW * kStageBytes + (FUSED ? 0 : MP * kXRowBytes);
+    constexpr int CPT = (kKC * kBN / 8) / kStThreads;          // 16-byte weight chunks per thread and stage (2)
     extern __shared__ __align__(128) unsigned char smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int KS = gridDim.y, rank = blockIdx.y;
@@ -72,103 +92,186 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
     const int n_stages = k_end > k_begin ? (k_end - k_begin + kKC - 1) / kKC : 0;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
 
-    // copy assignments of this thread: chunk c = tid + 128*i -> row c/16, 16-byte column c%16;
-    // `buf` is the ring slot of stage s (s % nst, tracked by the caller)
-    auto issue_w = [&](int s, int buf) {
-        if (s < n_stages) {
-            const int k0 = k_begin + s * kKC;
-            const uint32_t sbase = smem_base + (uint32_t)(buf * STAGE);
+    // Copy assignments, fixed for the whole kernel: chunk c = tid + 256*i is row c/16 of the stage,
+    // 16-byte column c%16.  Source pointers advance by 32 rows per stage; destinations are offsets
+    // inside a stage (XOR-swizzled by the row).
+    const __half* wsrc[NW][CPT];
+    uint32_t wdst[CPT];
+    int wrow[CPT];
+    bool wcol_ok[CPT];
 #pragma unroll
-            for (int w = 0; w < NW; w++) {
-                const __half* W = w == 0 ? W0 : W1;
+    for (int i = 0; i < CPT; i++) {
+        const int c = tid + kStThreads * i;
+        const int row = c >> 4, c16 = c & 15;
+        const int col = n0 + c16 * 8;
+        wrow[i] = row;
+        wcol_ok[i] = col < N;
+        wdst[i] = row * (kBN * 2) + ((c16 ^ (row & 7)) << 4);
+        const size_t off = (size_t)(k_begin + row) * N + (wcol_ok[i] ? col : 0);
+        wsrc[0][i] = W0 + off;
+        if (DUAL) wsrc[NW - 1][i] = W1 + off;
+    }
+    const size_t wstep = (size_t)kKC * N;
+    // activations: thread tid < 4*MP copies 16 bytes of row tid/4
+    const bool x_thread = !FUSED && tid < MP * 4;
+    const int x_part = tid & 3;
+    const __half* xsrc = FUSED ? x : x + (size_t)min(tid >> 2, M - 1) * K + k_begin + x_part * 8;
+    const uint32_t xdst = NW * kStageBytes + (tid >> 2) * kXRowBytes + x_part * 16;
+
+    int w_issued = 0, x_issued = 0;  // stages whose copies have been issued
+    auto issue_w = [&](uint32_t sbase) {
+        if (w_issued < n_stages) {
+            const int rows_left = k_end - (k_begin + w_issued * kKC);
 #pragma unroll
-                for (int i = 0; i < (kKC * kBN / 8) / kStThreads; i++) {
-                    const int c = tid + kStThreads * i;
-                    const int row = c >> 4, c16 = c & 15;
-                    const int k = k0 + row, col = n0 + c16 * 8;
-                    const bool ok = k < k_end && col < N;
-                    const __half* src = ok ? W + (size_t)k * N + col : W;
-                    const uint32_t dst = sbase + w * kStageBytes + row * (kBN * 2) + ((c16 ^ (row & 7)) << 4);
-                    cp_async16(dst, src, ok ? 16 : 0);
+            for (int w = 0; w < NW; w++)
+#pragma unroll
+                for (int i = 0; i < CPT; i++) {
+                    const bool ok = wcol_ok[i] && wrow[i] < rows_left;
+                    cp_async16(sbase + w * kStageBytes + wdst[i], ok ? (const void*)wsrc[w][i] : (const void*)W0, ok ? 16 : 0);
+                    wsrc[w][i] += wstep;
                 }
-            }
         }
+        w_issued++;
     };
-    // activations x[0..MP)[k0..k0+32): MP rows of four 16-byte chunks
-    auto issue_x = [&](int s, int buf) {
-        if (s < n_stages) {
-            const int k0 = k_begin + s * kKC;
-            const uint32_t sbase = smem_base + (uint32_t)(buf * STAGE);
-            for (int c = tid; c < MP * 4; c += kStThreads) {
-                const int row = c >> 2, part = c & 3;
-                const int k = k0 + part * 8;
-                const bool ok = k < k_end;
-                const __half* src = ok ? x + (size_t)min(row, M - 1) * K + k : x;
-                cp_async16(sbase + NW * kStageBytes + row * kXRowBytes + part * 16, src, ok ? 16 : 0);
-            }
+    auto issue_x = [&](uint32_t sbase) {
+        if (x_issued < n_stages && x_thread) {
+            const bool ok = k_begin + x_issued * kKC + x_part * 8 < k_end;
+            cp_async16(sbase + xdst, ok ? (const void*)xsrc : (const void*)x, ok ? 16 : 0);
+            xsrc += kKC;
         }
+        x_issued++;
     };
 
-    float acc[NW][2][MB][4];
+    float acc[NW][MB][4];
 #pragma unroll
     for (int w = 0; w < NW; w++)
 #pragma unroll
-        for (int ng = 0; ng < 2; ng++)
+        for (int mb = 0; mb < MB; mb++)
 #pragma unroll
-            for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) acc[w][ng][mb][e] = 0.f;
+            for (int e = 0; e < 4; e++) acc[w][mb][e] = 0.f;
 
     // The weights do not depend on the kernel that ran before this one, the activations do:
     // fill the ring with weights first and only then wait for the producer of x (programmatic
     // dependent launch; a no-op for a plain launch).  The next kernel in the stream is released
     // after the main loop, so that its prologue overlaps this kernel's reduction but its blocks
     // do not take shared memory from this kernel's ring.
-    for (int s = 0; s < nst - 1; s++) issue_w(s, s);
-    pdl_wait();
     for (int s = 0; s < nst - 1; s++) {
-        issue_x(s, s);
-        cp_async_commit();  // group 0 also carries every weight copy issued above
+        issue_w(smem_base + (uint32_t)(s * STAGE));
+        if (FUSED) cp_async_commit();
     }
-    int buf = 0, fill = nst - 1;  // slot being consumed, slot being refilled
+    pdl_wait();
+    // FUSED: normalised activations of this block's K range, [MP][xn_ld] halfs behind the ring
+    const int kc = stages_per_block * kKC;               // K range of a block (multiple of 32)
+    const int xn_ld = kc + 8;                            // row stride in halfs: an odd number of 16-byte units
+    __half* xn = reinterpret_cast<__half*>(smem + (size_t)nst * STAGE);
+    if (FUSED) {
+        __shared__ float inv_rms[MP];
+        // one warp per token row: r = x + residual + bias over the whole row, sum of squares by shuffles
+        for (int m = warp; m < MP; m += kStThreads / 32) {
+            const int mr = min(m, M - 1);
+            const __half* xr = x ? x + (size_t)mr * K : nullptr;
+            const __half* rr = fn.residual + (size_t)mr * K;
+            float ss = 0.f;
+            // loads are issued eight vectors at a time before any of them is used: the row comes
+            // from L2 and a load-use-load chain would cost one L2 round trip per vector
+            constexpr int NB = 8;
+            const int nv = K / 8;
+            for (int i0 = lane; i0 < nv; i0 += 32 * NB) {
+                uint4 rv[NB], xv[NB], bv[NB];
+#pragma unroll
+                for (int j = 0; j < NB; j++) {
+                    const int i = i0 + 32 * j;
+                    const bool in = i < nv;
+                    rv[j] = in ? *reinterpret_cast<const uint4*>(rr + (size_t)i * 8) : make_uint4(0, 0, 0, 0);
+                    xv[j] = (in && xr) ? *reinterpret_cast<const uint4*>(xr + (size_t)i * 8) : make_uint4(0, 0, 0, 0);
+                    bv[j] = (in && xr && fn.bias) ? *reinterpret_cast<const uint4*>(fn.bias + (size_t)i * 8)
+                                                  : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int j = 0; j < NB; j++) {
+                    const int i = i0 + 32 * j;
+                    if (i >= nv) break;
+                    float v[8], a[8], c[8];
+                    Vec16<__half>::unpack(rv[j], v);
+                    Vec16<__half>::unpack(xv[j], a);
+                    Vec16<__half>::unpack(bv[j], c);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        v[e] = v[e] + a[e] + c[e];
+                        ss = fmaf(v[e], v[e], ss);
+                    }
+                    const int k = i * 8;
+                    if (k >= k_begin && k < k_end) {
+                        const uint4 packed = Vec16<__half>::pack(v);
+                        *reinterpret_cast<uint4*>(xn + (size_t)m * xn_ld + (k - k_begin)) = packed;
+                        if (blockIdx.x == 0 && fn.residual_out && m < M)
+                            *reinterpret_cast<uint4*>(fn.residual_out + (size_t)m * K + k) = packed;
+                    }
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) inv_rms[m] = rsqrtf(ss / (float)K + fn.eps);
+        }
+        __syncthreads();
+        const int nvec = (k_end - k_begin) / 8;
+        for (int idx = tid; idx < MP * nvec; idx += kStThreads) {
+            const int m = idx / nvec, i = idx % nvec;
+            float v[8], gmm[8];
+            Vec16<__half>::load(xn + (size_t)m * xn_ld + i * 8, v);
+            Vec16<__half>::load(fn.gamma + k_begin + i * 8, gmm);
+            const float inv = inv_rms[m];
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = gmm[e] * v[e] * inv;
+            *reinterpret_cast<uint4*>(xn + (size_t)m * xn_ld + i * 8) = Vec16<__half>::pack(v);
+        }
+        // visibility to the other warps: the barrier at the top of the main loop
+    } else {
+        for (int s = 0; s < nst - 1; s++) {
+            issue_x(smem_base + (uint32_t)(s * STAGE));
+            cp_async_commit();  // group 0 also carries every weight copy issued above
+        }
+    }
+    uint32_t cons = 0, fill = (uint32_t)((nst - 1) * STAGE);  // byte offsets of the slot consumed / refilled
+    const uint32_t ring_bytes = (uint32_t)(nst * STAGE);
 
     // ldmatrix source of this lane inside a 16-row step: matrix m = lane/8 -> rows (m/2)*8 + lane%8,
-    // columns +8 for odd m
+    // columns +8 for odd m; this warp owns columns 16*warp .. 16*warp+15 of the tile
     const int lm_row = ((lane >> 4) << 3) + (lane & 7);
-    const int lm_col16 = (lane >> 3) & 1;
+    const int lm_c16 = warp * 2 + ((lane >> 3) & 1);
+    const uint32_t lm_off0 = lm_row * (kBN * 2) + ((lm_c16 ^ (lm_row & 7)) << 4);          // rows 0..15
+    const uint32_t lm_off1 = (16 + lm_row) * (kBN * 2) + ((lm_c16 ^ (lm_row & 7)) << 4);   // rows 16..31
+    const uint32_t xb_off = NW * kStageBytes + g * kXRowBytes + 4 * t;
 
     for (int s = 0; s < n_stages; s++) {
         cp_async_wait_dyn(nst - 2);
         __syncthreads();
-        issue_w(s + nst - 1, fill);
-        issue_x(s + nst - 1, fill);
+        issue_w(smem_base + fill);
+        issue_x(smem_base + fill);
         cp_async_commit();
-        const uint32_t sbase = smem_base + (uint32_t)(buf * STAGE);
-        const unsigned char* xs = smem + buf * STAGE + NW * kStageBytes;
-        buf = buf + 1 == nst ? 0 : buf + 1;
-        fill = fill + 1 == nst ? 0 : fill + 1;
+        const uint32_t sbase = smem_base + cons;
+        const unsigned char* xs = FUSED ? reinterpret_cast<const unsigned char*>(xn) + (size_t)g * xn_ld * 2 + (size_t)s * kKC * 2 + 4 * t
+                                        : smem + cons + xb_off;
+        const int x_row_bytes = FUSED ? xn_ld * 2 : kXRowBytes;
+        cons = cons + STAGE == ring_bytes ? 0 : cons + STAGE;
+        fill = fill + STAGE == ring_bytes ? 0 : fill + STAGE;
 #pragma unroll
         for (int kk = 0; kk < 2; kk++) {
             uint32_t xb[MB][2];
 #pragma unroll
             for (int mb = 0; mb < MB; mb++) {
-                const unsigned char* p = xs + (8 * mb + g) * kXRowBytes + (16 * kk + 2 * t) * 2;
+                const unsigned char* p = xs + 8 * mb * x_row_bytes + 32 * kk;
                 xb[mb][0] = *reinterpret_cast<const uint32_t*>(p);
                 xb[mb][1] = *reinterpret_cast<const uint32_t*>(p + 16);
             }
-            const int row = 16 * kk + lm_row;
 #pragma unroll
-            for (int w = 0; w < NW; w++)
+            for (int w = 0; w < NW; w++) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, sbase + w * kStageBytes + (kk ? lm_off1 : lm_off0));
+                // ldmatrix order is (n 0-7, k 0-7), (n 8-15, k 0-7), (n 0-7, k 8-15), (n 8-15, k 8-15)
+                // = a0, a1, a2, a3 of the mma "row" operand
 #pragma unroll
-                for (int ng = 0; ng < 2; ng++) {
-                    const int c16 = warp * 4 + ng * 2 + lm_col16;
-                    uint32_t a[4];
-                    ldmatrix_x4_trans(a, sbase + w * kStageBytes + row * (kBN * 2) + ((c16 ^ (row & 7)) << 4));
-                    // ldmatrix order is (n 0-7, k 0-7), (n 8-15, k 0-7), (n 0-7, k 8-15), (n 8-15, k 8-15)
-                    // = a0, a1, a2, a3 of the mma "row" operand
-#pragma unroll
-                    for (int mb = 0; mb < MB; mb++) mma16816(acc[w][ng][mb], a, xb[mb][0], xb[mb][1]);
-                }
+                for (int mb = 0; mb < MB; mb++) mma16816(acc[w][mb], a, xb[mb][0], xb[mb][1]);
+            }
         }
     }
     cp_async_wait<0>();
@@ -180,15 +283,13 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
 #pragma unroll
     for (int w = 0; w < NW; w++)
 #pragma unroll
-        for (int ng = 0; ng < 2; ng++)
+        for (int mb = 0; mb < MB; mb++)
 #pragma unroll
-            for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int tok = 8 * mb + 2 * t + (e & 1);
-                    const int c = warp * 32 + ng * 16 + g + ((e & 2) ? 8 : 0);
-                    red[(w * MP + tok) * kRedLd + c] = acc[w][ng][mb][e];
-                }
+            for (int e = 0; e < 4; e++) {
+                const int tok = 8 * mb + 2 * t + (e & 1);
+                const int c = warp * 16 + g + ((e & 2) ? 8 : 0);
+                red[(w * MP + tok) * kRedLd + c] = acc[w][mb][e];
+            }
     cluster.sync();
     const int per_rank = (MP * kBN + KS - 1) / KS;
     const int e_begin = rank * per_rank, e_end = min(e_begin + per_rank, MP * kBN);
@@ -214,8 +315,9 @@ static int staged_slots(Kern kern, int ks, int nst, size_t smem, int col_blocks)
 {
     // one table for every instantiation (they share the function-pointer type): the kernel is
     // part of the key
-    static std::map<std::tuple<const void*, int, int>, int> cache;
-    const auto key = std::make_tuple((const void*)kern, ks, nst);
+    static std::map<std::tuple<const void*, int, size_t>, int> cache;
+    const auto key = std::make_tuple((const void*)kern, ks, smem);
+    (void)nst;
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     cudaLaunchConfig_t cfg = {};
@@ -238,13 +340,13 @@ static int staged_slots(Kern kern, int ks, int nst, size_t smem, int col_blocks)
     return clusters * ks;
 }
 
-template <int MB, bool DUAL>
+template <int MB, bool DUAL, bool FUSED>
 static cudaError_t launch_staged(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K,
-                                 cudaStream_t st)
+                                 const FusedNormArgs& fn, cudaStream_t st)
 {
-    auto kern = skinny_kn_staged_kernel<MB, DUAL>;
+    auto kern = skinny_kn_staged_kernel<MB, DUAL, FUSED>;
     constexpr int NW = DUAL ? 2 : 1;
-    constexpr size_t stage = (size_t)NW * kStageBytes + 8 * MB * kXRowBytes;
+    constexpr size_t stage = (size_t)NW * kStageBytes + (FUSED ? 0 : 8 * MB * kXRowBytes);
     constexpr size_t red = (size_t)NW * 8 * MB * kRedLd * sizeof(float);
     constexpr size_t smem_cap = 226 * 1024;
     static bool attr_set = false;
@@ -257,31 +359,48 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     }
     const int col_blocks = (N + kBN - 1) / kBN;
     const int total_stages = (K + kKC - 1) / kKC;
-    auto smem_for = [&](int nst) { return std::max(stage * nst, red); };
-    // Plan.  Measured on B200 with a copy-only version of this tiling: about 1.7 blocks per SM
-    // (256 blocks) with a ring of 8 stages already streams at the ceiling of the staged path;
-    // more, smaller blocks are slower (each pays its own pipeline fill and reduction), fewer
-    // blocks need deeper rings.  So: split K so that the grid lands near 1.75 blocks per SM,
-    // keep every block resident (one wave), and give each ring what shared memory allows.
-    const int target_blocks = num_sms() * 7 / 4;
-    int best_ks = 1;
+    // Plan: the K split (= cluster size, 1..8) and ring depth that keep the most bytes in flight
+    // while every block is resident at once (residency asked from the runtime, because clusters
+    // do not always pack the SMs of a GPC fully).  A sweep over (split, depth) on B200 for the
+    // four projection shapes of the 7B model agrees with this rule within a microsecond.
+    int best_ks = 1, best_nst = 3;
     {
-        double best_d = 1e30;
+        double best_inflight = -1.0;
         for (int ks = 1; ks <= 8; ks++) {
             const int per = (total_stages + ks - 1) / ks;
             if (ks > 1 && per < 4) break;
-            const double d = fabs(log((double)col_blocks * ks / (double)target_blocks));
-            if (d < best_d) {
-                best_d = d;
-                best_ks = ks;
+            const long total = (long)col_blocks * ks;
+            const size_t xn_b = FUSED ? (size_t)8 * MB * (per * kKC + 8) * sizeof(__half) : 0;
+            for (int nst = std::min(12, std::max(3, per + 1)); nst >= 3; nst--) {
+                const size_t smem = std::max(stage * nst, red) + xn_b;
+                if (smem > smem_cap) continue;
+                if (staged_slots(kern, ks, nst, smem, col_blocks) < total) continue;
+                // FUSED: every block redoes the row statistics, so fewer blocks are better there
+                const double inflight = (double)total * (nst - 1) * (double)(NW * kStageBytes) / (FUSED ? (double)ks : 1.0);
+                if (inflight > best_inflight * 1.02) {
+                    best_inflight = inflight;
+                    best_ks = ks;
+                    best_nst = nst;
+                }
+                break;  // shallower rings for this split only lose
             }
         }
+        if (best_inflight < 0) {  // nothing fits in one wave: smallest blocks, shallow ring
+            best_ks = 1;
+            best_nst = 3;
+        }
     }
-    const int per_block = (total_stages + best_ks - 1) / best_ks;
-    const long total = (long)col_blocks * best_ks;
-    int best_nst = std::min(12, std::max(3, per_block + 1));
-    best_nst = std::min<int>(best_nst, (int)(smem_cap / stage));
-    while (best_nst > 3 && staged_slots(kern, best_ks, best_nst, smem_for(best_nst), col_blocks) < total) best_nst--;
+    if (const char* e = getenv("ONELLM_DEV_STAGED_PLAN")) {  // development sweep: "ks,nst"
+        int ks = 0, nst = 0;
+        if (sscanf(e, "%d,%d", &ks, &nst) == 2 && ks >= 1 && ks <= 8 && nst >= 3) {
+            best_ks = ks;
+            best_nst = nst;
+        }
+    }
+    const int per_block_final = (total_stages + best_ks - 1) / best_ks;
+    const size_t xn_final = FUSED ? (size_t)8 * MB * (per_block_final * kKC + 8) * sizeof(__half) : 0;
+    const size_t smem_final = std::max(stage * best_nst, red) + xn_final;
+    if (smem_final > smem_cap) return cudaErrorInvalidConfiguration;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -292,27 +411,64 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.gridDim = dim3(col_blocks, best_ks, 1);
     cfg.blockDim = dim3(kStThreads);
-    cfg.dynamicSmemBytes = smem_for(best_nst);
+    cfg.dynamicSmemBytes = smem_final;
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, (total_stages + best_ks - 1) / best_ks, best_nst);
+    return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, per_block_final, best_nst, fn);
 }
 
 // One pass of at most 64 tokens.  Called from skinny_gemm.cu.
 cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
                                       int K, bool dual, cudaStream_t st)
 {
+    const FusedNormArgs none = {nullptr, nullptr, nullptr, nullptr, 0.f};
     if (dual) {
-        if (M <= 8) return launch_staged<1, true>(x, W0, W1, y, M, N, K, st);
-        if (M <= 16) return launch_staged<2, true>(x, W0, W1, y, M, N, K, st);
-        if (M <= 32) return launch_staged<4, true>(x, W0, W1, y, M, N, K, st);
-        return launch_staged<8, true>(x, W0, W1, y, M, N, K, st);
+        if (M <= 8) return launch_staged<1, true, false>(x, W0, W1, y, M, N, K, none, st);
+        if (M <= 16) return launch_staged<2, true, false>(x, W0, W1, y, M, N, K, none, st);
+        if (M <= 32) return launch_staged<4, true, false>(x, W0, W1, y, M, N, K, none, st);
+        return launch_staged<8, true, false>(x, W0, W1, y, M, N, K, none, st);
     }
-    if (M <= 8) return launch_staged<1, false>(x, W0, nullptr, y, M, N, K, st);
-    if (M <= 16) return launch_staged<2, false>(x, W0, nullptr, y, M, N, K, st);
-    if (M <= 32) return launch_staged<4, false>(x, W0, nullptr, y, M, N, K, st);
-    return launch_staged<8, false>(x, W0, nullptr, y, M, N, K, st);
+    if (M <= 8) return launch_staged<1, false, false>(x, W0, nullptr, y, M, N, K, none, st);
+    if (M <= 16) return launch_staged<2, false, false>(x, W0, nullptr, y, M, N, K, none, st);
+    if (M <= 32) return launch_staged<4, false, false>(x, W0, nullptr, y, M, N, K, none, st);
+    return launch_staged<8, false, false>(x, W0, nullptr, y, M, N, K, none, st);
 }
 
 }  // namespace onellm
+
+using namespace onellm;
+
+extern "C" int onellm_add_residual_rmsnorm_gemm(int dtype, const void* x, const void* residual, const void* bias,
+                                                const void* gamma, float eps, void* residual_out, const void* W,
+                                                const void* Wu, void* y, int M, int N, int K, void* stream)
+{
+    ONELLM_REQUIRE(residual && gamma && W && y, ONELLM_ERR_ARG, "add_residual_rmsnorm_gemm: null pointer");
+    ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "add_residual_rmsnorm_gemm: only F16 is implemented");
+    ONELLM_REQUIRE(M >= 0 && N > 0 && K > 0, ONELLM_ERR_ARG, "add_residual_rmsnorm_gemm: bad size");
+    ONELLM_REQUIRE(M <= 16, ONELLM_ERR_UNSUPPORTED,
+                   "add_residual_rmsnorm_gemm: covers M <= 16; use onellm_add_residual_rmsnorm then onellm_gemm");
+    ONELLM_REQUIRE(K % 16 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED,
+                   "add_residual_rmsnorm_gemm: need K %% 16 == 0 and N %% 8 == 0");
+    ONELLM_REQUIRE(!x || residual_out, ONELLM_ERR_ARG, "add_residual_rmsnorm_gemm: residual_out is required when x is given");
+    ONELLM_REQUIRE(residual_out != residual, ONELLM_ERR_ARG,
+                   "add_residual_rmsnorm_gemm: residual_out must not alias residual");
+    ONELLM_REQUIRE(aligned16(residual) && aligned16(gamma) && aligned16(W) && aligned16(y) && (!x || aligned16(x)) &&
+                       (!bias || aligned16(bias)) && (!Wu || aligned16(Wu)) && (!residual_out || aligned16(residual_out)),
+                   ONELLM_ERR_ARG, "add_residual_rmsnorm_gemm: pointers must be 16-byte aligned");
+    if (M == 0) return ONELLM_OK;
+    const FusedNormArgs fn = {(const __half*)residual, (const __half*)bias, (const __half*)gamma,
+                              x ? (__half*)residual_out : nullptr, eps};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const __half *xh = (const __half*)x, *w0 = (const __half*)W, *w1 = (const __half*)Wu;
+    __half* yh = (__half*)y;
+    cudaError_t e;
+    if (Wu)
+        e = M <= 8 ? launch_staged<1, true, true>(xh, w0, w1, yh, M, N, K, fn, st)
+                   : launch_staged<2, true, true>(xh, w0, w1, yh, M, N, K, fn, st);
+    else
+        e = M <= 8 ? launch_staged<1, false, true>(xh, w0, nullptr, yh, M, N, K, fn, st)
+                   : launch_staged<2, false, true>(xh, w0, nullptr, yh, M, N, K, fn, st);
+    ONELLM_REQUIRE(e == cudaSuccess, ONELLM_ERR_CUDA, "add_residual_rmsnorm_gemm: %s", cudaGetErrorString(e));
+    return ONELLM_OK;
+}

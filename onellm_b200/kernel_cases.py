@@ -19,7 +19,7 @@ H_, D_, HID, INTER, VOCAB = 32, 128, 4096, 11008, 32000
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm"])
+    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm", "gate_up_fused", "qkv_fused", "norm8"])
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2040)
@@ -42,6 +42,22 @@ def main():
         out = torch.empty(B, N, device="cuda", dtype=torch.float16)
         fn = lambda i: ob.gemm(ob.F16, x, w[i], out, B, N, K, ob.W_KN)
         nbytes = K * N * 2 + B * K * 2 + B * N * 2
+    elif a.case in ("gate_up_fused", "qkv_fused"):
+        N = INTER if a.case == "gate_up_fused" else 3 * HID
+        x, r = torch.randn(B, HID, device="cuda").half(), torch.randn(B, HID, device="cuda").half()
+        r2 = torch.empty_like(r)
+        g = torch.ones(HID, device="cuda", dtype=torch.float16)
+        w = [rnd(HID, N) for _ in range(rot)]
+        wu = [rnd(HID, N) for _ in range(rot)] if a.case == "gate_up_fused" else [None] * rot
+        out = torch.empty(B, N, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.add_residual_rmsnorm_gemm(ob.F16, x, r, None, g, 1e-5, r2, w[i], wu[i], out, B, N, HID)
+        nbytes = (2 if a.case == "gate_up_fused" else 1) * HID * N * 2 + 3 * B * HID * 2 + B * N * 2
+    elif a.case == "norm8":
+        xs = [torch.randn(B, HID, device="cuda").half() for _ in range(rot)]
+        rs = [torch.randn(B, HID, device="cuda").half() for _ in range(rot)]
+        g = torch.ones(HID, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.add_residual_rmsnorm(ob.F16, rs[i], xs[i], None, g, 1e-5, B, HID)
+        nbytes = 4 * B * HID * 2
     elif a.case == "lm_head":
         x, w = torch.randn(B, HID, device="cuda").half(), [rnd(VOCAB, HID) for _ in range(2)]
         rot = 2

@@ -319,3 +319,39 @@ def test_sampling_matches_oracle_given_same_uniform(ob, cuda, orc, K, temp, lite
         u2 = torch.zeros(B, device="cuda")
         ob.topk_sample(torch.from_numpy(ri).cuda(), torch.from_numpy(rv).cuda(), B, K, temp, step, V, 10, out, None, None, u2)
         assert torch.equal(u, u2)
+
+
+@pytest.mark.parametrize("M", [1, 8, 16])
+@pytest.mark.parametrize("N,K,dual,with_x,with_bias", [
+    (12288, 4096, False, True, False), (12288, 4096, False, False, False), (11008, 4096, True, True, True),
+    (1376, 4096, True, True, False), (15360, 5120, False, True, True), (1728, 5120, True, True, False),
+])
+def test_add_residual_rmsnorm_gemm_fused(ob, cuda, orc, M, N, K, dual, with_x, with_bias):
+    """One launch = fused add-bias-residual RMSNorm, then the projection (and SwiGLU)."""
+    torch = cuda
+    rng = np.random.default_rng(M + N)
+    x = _round(rng.standard_normal((M, K)), "f16") if with_x else None
+    r = _round(rng.standard_normal((M, K)), "f16")
+    b = _round(0.1 * rng.standard_normal(K), "f16") if with_bias else None
+    g = _round(1 + 0.1 * rng.standard_normal(K), "f16")
+    W = _round(0.02 * rng.standard_normal((K, N)), "f16")
+    Wu = _round(0.02 * rng.standard_normal((K, N)), "f16") if dual else None
+    if with_x:
+        xn, r_new = orc.add_residual_rmsnorm(r, x, b, g, 1e-5)
+    else:
+        xn, r_new = orc.rmsnorm(r, g, 1e-5), r
+    xn = _round(xn, "f16")
+    ref = orc.swiglu2(orc.gemm(xn, W), orc.gemm(xn, Wu)) if dual else orc.gemm(xn, W)
+    y = torch.zeros(M, N, device="cuda", dtype=torch.float16)
+    r_out = torch.zeros(M, K, device="cuda", dtype=torch.float16)
+    d_r = _dev(torch, r, "f16")
+    ob.add_residual_rmsnorm_gemm(ob.F16, None if x is None else _dev(torch, x, "f16"), d_r,
+                                 None if b is None else _dev(torch, b, "f16"), _dev(torch, g, "f16"), 1e-5, r_out,
+                                 _dev(torch, W, "f16"), None if Wu is None else _dev(torch, Wu, "f16"), y, M, N, K)
+    assert rel_err(y.float().cpu().numpy(), ref) < 2e-3  # normalised activations are rounded to fp16 in both arms
+    assert np.array_equal(d_r.float().cpu().numpy(), r)  # the input residual is not touched
+    if with_x:
+        assert rel_err(r_out.float().cpu().numpy(), r_new) < TOL["f16"]
+    with pytest.raises(ob.OnellmError):
+        ob.add_residual_rmsnorm_gemm(ob.F16, d_r, d_r, None, _dev(torch, g, "f16"), 1e-5, d_r, _dev(torch, W, "f16"), None,
+                                     y, M, N, K)
