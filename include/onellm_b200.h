@@ -146,6 +146,10 @@ ONELLM_API int onellm_add_residual_rmsnorm(int dtype, void* residual, void* deco
 ONELLM_API int onellm_gemm(int dtype, const void* x, const void* W, void* y, int M, int N, int K,
                            int w_layout, void* stream);
 
+/* 1 if a block of the tensor-core GEMM gave up a bounded wait since the last call (the flag is cleared),
+ * 0 otherwise, -1 if it cannot be read.  Such a block skips its stores: the output is then incomplete. */
+ONELLM_API int onellm_gemm_timeout_flag(void);
+
 /* Gate and up projections with SwiGLU applied on the way out:
  *     out[M,I] = silu(x.Wg) * (x.Wu),   Wg, Wu [K,I]
  * Replaces the gate GEMM, up GEMM and launchAct of LLaMAFFNLayer::forward

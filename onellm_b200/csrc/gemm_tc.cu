@@ -1,21 +1,289 @@
-// Tiled tensor-core projection for M > 64 (context phase).
+// Context-phase projections (M > 64 tokens) on the 5th-generation tensor cores of sm_100a.
+//
+// Replaces the cuBLAS GEMM behind launchLinearGemm (src/kernels/qkv_linear.cu:8-65,
+// src/kernels/cublas_wrapper.cc:45-90 of the reference) for prefill shapes: y[M,N] = x[M,K] . W with
+// W [K,N] (the layer weights, N contiguous) or W [N,K] (the LM head), fp16 in, fp32 accumulate.
+//
+// One 128 x 128 output tile per block.  A producer thread streams 64-deep K slices of both
+// operands into a ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle;
+// no cluster multicast anywhere); an MMA thread issues tcgen05.mma (M = 128, N = 128, K = 16,
+// kind::f16) with the accumulator in tensor memory and releases each stage with tcgen05.commit;
+// after the last slice all four warps read the accumulator with tcgen05.ld, convert and store.
+// The [K,N] weight is used as it lies in memory: it is the "MN-major" B operand of the MMA
+// (two 64-column TMA boxes per stage), so no transposed copy of the weights is ever made.
+// Every wait on an mbarrier is bounded; on a time-out the block records it in a device flag,
+// skips its stores, frees its tensor memory and exits.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
 
 namespace onellm {
 
-int gemm_f16_skinny(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout,
-                    cudaStream_t st);
+constexpr int kTcBM = 128, kTcBN = 128, kTcBK = 64;
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 128;
+constexpr int kTcATile = kTcBM * kTcBK * 2;        // 16 KB: 128 rows x 128 bytes
+constexpr int kTcBTile = kTcBN * kTcBK * 2;        // 16 KB: [K,N] two boxes of 64 k-rows x 128 bytes; [N,K] 128 rows x 128 bytes
+constexpr int kTcStageBytes = kTcATile + kTcBTile;
+constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr uint32_t kSpinLimit = 1u << 24;  // ~0.3 s of polling
 
-int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout,
-                   cudaStream_t st)
+__device__ int g_tc_timeout_flag;  // set when a bounded wait gave up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
-    // TEMPORARY: 64-token passes of the weight-streaming kernel until the tiled kernel lands.
-    for (int m0 = 0; m0 < M; m0 += 64) {
-        const int mm = M - m0 < 64 ? M - m0 : 64;
-        const int rc = gemm_f16_skinny(x + (size_t)m0 * K, W, y + (size_t)m0 * N, mm, N, K, w_layout, st);
-        if (rc) return rc;
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// bounded wait; returns false (and raises the flag) when the phase never completes
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kSpinLimit; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
     }
+    atomicExch(&g_tc_timeout_flag, 1);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+// shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
+        "[%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// W_NK = false: W [K,N] (B operand MN-major);  W_NK = true: W [N,K] (B operand K-major).
+// grid = (ceil(N/128), ceil(M/128)).
+template <bool W_NK>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               __half* __restrict__ y, int M, int N, int K)
+{
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment for the 128-byte swizzle pattern
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTcStages * kTcStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 1);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcStages), accum_bar = smem_u32(bars + 2 * kTcStages);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kTcBN, m0 = blockIdx.y * kTcBM;
+    const int k_steps = (K + kTcBK - 1) / kTcBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTcStages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    pdl_wait();  // x comes from the previous kernel in the stream
+
+    bool ok = true;
+    if (warp == 0 && lane == 0) {
+        // producer: one 64-deep slice of A and of B per stage
+        for (int ks = 0; ks < k_steps && ok; ks++) {
+            const int s = ks % kTcStages;
+            if (ks >= kTcStages) ok = mbar_wait(empty0 + 8 * s, ((ks / kTcStages) - 1) & 1);
+            if (!ok) break;
+            const uint32_t a_dst = smem_u32(smem + s * kTcStageBytes), b_dst = a_dst + kTcATile;
+            mbar_expect_tx(full0 + 8 * s, kTcStageBytes);
+            tma_load_2d(a_dst, &map_a, ks * kTcBK, m0, full0 + 8 * s);
+            if (W_NK) {
+                tma_load_2d(b_dst, &map_b, ks * kTcBK, n0, full0 + 8 * s);
+            } else {
+                tma_load_2d(b_dst, &map_b, n0, ks * kTcBK, full0 + 8 * s);
+                tma_load_2d(b_dst + kTcBTile / 2, &map_b, n0 + 64, ks * kTcBK, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // instruction descriptor: D = f32, A = B = f16, A K-major, B MN-major unless W_NK, N = 128, M = 128
+        const uint32_t idesc = (1u << 4) | ((W_NK ? 0u : 1u) << 16) | ((uint32_t)(kTcBN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
+        for (int ks = 0; ks < k_steps && ok; ks++) {
+            const int s = ks % kTcStages;
+            ok = mbar_wait(full0 + 8 * s, (ks / kTcStages) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_addr = smem_u32(smem + s * kTcStageBytes), b_addr = a_addr + kTcATile;
+#pragma unroll
+            for (int kk = 0; kk < kTcBK / 16; kk++) {
+                // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; 16 k = 32 bytes further in the row
+                const uint64_t adesc = umma_desc(a_addr + kk * 32, 16, 1024);
+                // B [N,K]: same form.  B [K,N]: MN-major, 64-column chunks 8192 bytes apart (LBO), 8-row k groups
+                // 1024 bytes apart (SBO); 16 k = two groups further
+                const uint64_t bdesc = W_NK ? umma_desc(b_addr + kk * 32, 16, 1024) : umma_desc(b_addr + kk * 2048, kTcBTile / 2, 1024);
+                umma_f16(tmem_base, adesc, bdesc, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
+        }
+        if (ok) umma_commit(accum_bar);
+    }
+    // epilogue: every warp reads its 32 accumulator rows (TMEM lanes 32*warp ..)
+    __syncwarp();
+    ok = mbar_wait(accum_bar, 0) && ok;
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    pdl_launch_dependents();
+    if (ok) {
+        const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kTcBN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < M) {
+                __half* dst = y + (size_t)row * N + n0 + c0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (n0 + c0 + 8 * j < N) {  // N is a multiple of 8
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const __half2 h = __floats2half2_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                        *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 2) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D fp16 tensor map: `inner` contiguous elements, `outer` rows of `inner` elements; box {64, box_outer}; 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_outer)
+{
+    EncodeTiledFn enc = encode_tiled();
+    ONELLM_REQUIRE(enc, ONELLM_ERR_CUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * sizeof(__half)};
+    const cuuint32_t box[2] = {64, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    ONELLM_REQUIRE(r == CUDA_SUCCESS, ONELLM_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed with %d", (int)r);
     return ONELLM_OK;
 }
 
+int gemm_f16_skinny(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout, cudaStream_t st);
+
+int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout, cudaStream_t st)
+{
+    ONELLM_REQUIRE(K % 8 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED, "gemm: M > 64 needs K %% 8 == 0 and N %% 8 == 0 (K=%d N=%d)",
+                   K, N);
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, x, (uint64_t)K, (uint64_t)M, kTcBM);
+    if (rc) return rc;
+    const bool nk = w_layout == ONELLM_W_NK;
+    rc = nk ? make_map(&map_b, W, (uint64_t)K, (uint64_t)N, kTcBN) : make_map(&map_b, W, (uint64_t)N, (uint64_t)K, kTcBK);
+    if (rc) return rc;
+    static bool attr_set[2] = {false, false};
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[nk]) {
+            ONELLM_CUDA(nk ? cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes)
+                           : cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
+            attr_set[nk] = true;
+        }
+    }
+    const dim3 grid((N + kTcBN - 1) / kTcBN, (M + kTcBM - 1) / kTcBM);
+    ONELLM_REQUIRE(grid.y <= 65535, ONELLM_ERR_UNSUPPORTED, "gemm: M too large");
+    if (nk)
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<true>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, y, M, N, K));
+    else
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<false>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, y, M, N, K));
+    return ONELLM_OK;
+}
+
+// 1 when a tensor-core GEMM block gave up a bounded wait since the last call (and clears the flag).
+int gemm_tc_timeout_flag()
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_timeout_flag, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_tc_timeout_flag, &zero, sizeof(int));
+    return v;
+}
+
 }  // namespace onellm
+
+extern "C" int onellm_gemm_timeout_flag(void) { return onellm::gemm_tc_timeout_flag(); }

@@ -355,3 +355,21 @@ def test_add_residual_rmsnorm_gemm_fused(ob, cuda, orc, M, N, K, dual, with_x, w
     with pytest.raises(ob.OnellmError):
         ob.add_residual_rmsnorm_gemm(ob.F16, d_r, d_r, None, _dev(torch, g, "f16"), 1e-5, d_r, _dev(torch, W, "f16"), None,
                                      y, M, N, K)
+
+
+@pytest.mark.parametrize("M,N,K,nk", [
+    (128, 128, 64, False), (128, 128, 64, True), (256, 256, 256, False), (1024, 4096, 4096, False),
+    (1000, 12288, 4096, False), (65, 1376, 4096, False), (512, 4096, 11008, False), (300, 4096, 1376, False),
+    (192, 32000, 4096, True), (130, 1000, 512, True),
+])
+def test_gemm_f16_tensor_core_tiles(ob, cuda, orc, M, N, K, nk):
+    """M > 64: the tcgen05 / TMEM / TMA kernel, both weight layouts, ragged M, N and K tails."""
+    torch = cuda
+    rng = np.random.default_rng(M + N + K)
+    x = _round(rng.standard_normal((M, K)), "f16")
+    W = _round(0.02 * rng.standard_normal((N, K) if nk else (K, N)), "f16")
+    y = torch.full((M, N), 7.0, device="cuda", dtype=torch.float16)
+    ob.gemm(ob.F16, _dev(torch, x, "f16"), _dev(torch, W, "f16"), y, M, N, K, ob.W_NK if nk else ob.W_KN)
+    torch.cuda.synchronize()
+    assert ob.lib().onellm_gemm_timeout_flag() == 0
+    assert rel_err(y.float().cpu().numpy(), orc.gemm(x, W, w_is_nk=nk)) < TOL["f16"]
