@@ -182,6 +182,42 @@ ONELLM_API int onellm_embedding(int dtype, const int* ids, void* out, const void
                                 int hidden, int vocab, int* bad_id_flag, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Context phase, step 1: bias + RoPE on the packed QKV of `num_tokens` prompt tokens, K/V written
+ * straight into one layer's cache.
+ * Replaces launchAddFusedQKVBiasTransposeAndRoPE (src/kernels/qkv_bias_and_RoPE.h:6-14,
+ * qkv_bias_and_RoPE.cu:74-207) and launchAppendKVCache (src/kernels/append_to_kvcache.h:20-26,
+ * append_to_kvcache.cu:8-114) without the padded, transposed copies.
+ *   qkv [num_tokens, H+2Hkv, D] packed (no padding); q heads are rotated IN PLACE; bias [(H+2Hkv)*D] or NULL.
+ *   cu_seqlens [B+1] device ints: token offsets of the sequences (what launchCalPaddingoffset calls
+ *     cum_seqlens, src/kernels/cal_paddingoffset.cu:9-32); history_length [B] device ints.
+ *   Token i of sequence b has position history_length[b] + i (qkv_bias_and_RoPE.cu:138-143); its k
+ *   (rotated) and v go to cache row (b, kv_head, position) with the strides of onellm_decode_attn.
+ *   A position >= max_seq_len is not written and sets *overflow_flag (device int, may be NULL).
+ * F16 or F32.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_qkv_bias_rope_kvcache(int dtype, void* qkv, const void* bias, const int* cu_seqlens,
+                                            const int* history_length, void* k_cache, void* v_cache,
+                                            long cs_b, long cs_h, long cs_s, int num_tokens, int B, int H,
+                                            int Hkv, int D, int rot_dim, float rope_base, int max_seq_len,
+                                            int* overflow_flag, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Context phase, step 2: causal attention of the prompt tokens over the cache.
+ * Replaces launchTransposeKVCache, launchLinearStridedBatchGemm (Q.K^T and P.V),
+ * launchBuildCausalMasks, launchScaleMaskAndSoftmax and launchTransposeOutRemovePadding as chained in
+ * LLaMAContextAttentionLayer::forward (src/layers/attention/context_attention.cpp:134-148); no score
+ * matrix and no repeated KV are materialised.
+ *   q: rotated queries, token t / head h at q + t*q_ld + h*D (q_ld = (H+2Hkv)*D reads them in place
+ *   from the QKV buffer); out [num_tokens, H*D].  Token i of sequence b attends cache rows
+ *   0 .. history_length[b] + i of KV head h / (H/Hkv).  max_q_len = longest sequence of this call.
+ * F16, D = 64 or 128.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_context_attn(int dtype, const void* q, long q_ld, const void* k_cache, const void* v_cache,
+                                   long cs_b, long cs_h, long cs_s, const int* cu_seqlens,
+                                   const int* history_length, int B, int max_q_len, int H, int Hkv, int D,
+                                   float scale, void* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Row-wise top-K of logits [rows, vocab] (F32 or F16), values sorted descending, ties to
  * the lower column.  out_val float [rows,K], out_id int32 [rows,K] (column index, or
  * row*vocab + column when global_ids != 0 as the reference's beam-search kernel emits).

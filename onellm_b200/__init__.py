@@ -140,6 +140,23 @@ def embedding(dtype, ids, out, table, n_tokens, hidden, vocab, bad_id_flag=None,
                                   C.c_int(hidden), C.c_int(vocab), _p(bad_id_flag), _stream(stream)))
 
 
+def qkv_bias_rope_kvcache(dtype, qkv, bias, cu_seqlens, history_length, k_cache, v_cache, cs_b, cs_h, cs_s, num_tokens,
+                          B, H, Hkv, D, rot_dim, rope_base, max_seq_len, overflow_flag=None, stream=None):
+    _check(lib().onellm_qkv_bias_rope_kvcache(C.c_int(dtype), _p(qkv), _p(bias), _p(cu_seqlens), _p(history_length),
+                                              _p(k_cache), _p(v_cache), C.c_long(cs_b), C.c_long(cs_h), C.c_long(cs_s),
+                                              C.c_int(num_tokens), C.c_int(B), C.c_int(H), C.c_int(Hkv), C.c_int(D),
+                                              C.c_int(rot_dim), C.c_float(rope_base), C.c_int(max_seq_len),
+                                              _p(overflow_flag), _stream(stream)))
+
+
+def context_attn(dtype, q, q_ld, k_cache, v_cache, cs_b, cs_h, cs_s, cu_seqlens, history_length, B, max_q_len, H, Hkv, D,
+                 scale, out, stream=None):
+    _check(lib().onellm_context_attn(C.c_int(dtype), _p(q), C.c_long(q_ld), _p(k_cache), _p(v_cache), C.c_long(cs_b),
+                                     C.c_long(cs_h), C.c_long(cs_s), _p(cu_seqlens), _p(history_length), C.c_int(B),
+                                     C.c_int(max_q_len), C.c_int(H), C.c_int(Hkv), C.c_int(D), C.c_float(scale), _p(out),
+                                     _stream(stream)))
+
+
 def topk(dtype, logits, rows, vocab, K, out_val, out_id, global_ids=False, stream=None):
     _check(lib().onellm_topk(C.c_int(dtype), _p(logits), C.c_int(rows), C.c_int(vocab), C.c_int(K),
                              _p(out_val), _p(out_id), C.c_int(1 if global_ids else 0), _stream(stream)))

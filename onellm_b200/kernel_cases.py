@@ -19,7 +19,7 @@ H_, D_, HID, INTER, VOCAB = 32, 128, 4096, 11008, 32000
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm", "gate_up_fused", "qkv_fused", "norm8"])
+    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm", "gate_up_fused", "qkv_fused", "norm8", "prefill_qkv", "prefill_down", "prefill_gate", "prefill_lm"])
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2040)
@@ -52,6 +52,16 @@ def main():
         out = torch.empty(B, N, device="cuda", dtype=torch.float16)
         fn = lambda i: ob.add_residual_rmsnorm_gemm(ob.F16, x, r, None, g, 1e-5, r2, w[i], wu[i], out, B, N, HID)
         nbytes = (2 if a.case == "gate_up_fused" else 1) * HID * N * 2 + 3 * B * HID * 2 + B * N * 2
+    elif a.case.startswith("prefill_"):
+        T = 4096 if a.batch == 8 else a.batch
+        K, N, lay = {"prefill_qkv": (HID, 3 * HID, ob.W_KN), "prefill_down": (INTER, HID, ob.W_KN),
+                     "prefill_gate": (HID, INTER, ob.W_KN), "prefill_lm": (HID, VOCAB, ob.W_NK)}[a.case]
+        x = torch.randn(T, K, device="cuda").half()
+        w = [rnd(N, K) if lay == ob.W_NK else rnd(K, N) for _ in range(2)]
+        rot = 2
+        out = torch.empty(T, N, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.gemm(ob.F16, x, w[i], out, T, N, K, lay)
+        nbytes = 2 * T * N * K  # flops, reported as "GB/s" = GFLOP/s below
     elif a.case == "norm8":
         xs = [torch.randn(B, HID, device="cuda").half() for _ in range(rot)]
         rs = [torch.randn(B, HID, device="cuda").half() for _ in range(rot)]
@@ -96,7 +106,11 @@ def main():
     e1.record(st)
     st.synchronize()
     t = e0.elapsed_time(e1) / a.iters * 1e-3
-    print(f"{a.case}: {t * 1e6:.1f} us/launch, {nbytes / t / 1e9:.0f} GB/s algorithmic ({nbytes} bytes)")
+    if a.case.startswith("prefill_"):
+        print(f"{a.case}: {t * 1e6:.1f} us/launch, {nbytes / t / 1e12:.0f} TFLOP/s ({nbytes} flops), timeout flag "
+              f"{ob.lib().onellm_gemm_timeout_flag()}")
+    else:
+        print(f"{a.case}: {t * 1e6:.1f} us/launch, {nbytes / t / 1e9:.0f} GB/s algorithmic ({nbytes} bytes)")
 
 
 if __name__ == "__main__":
