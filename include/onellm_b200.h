@@ -285,6 +285,9 @@ ONELLM_API int onellm_llama_init_comm(onellm_llama* m, const void* id128);
 
 ONELLM_API int onellm_llama_set_sampling(onellm_llama* m, int top_k, float temperature, int literal_walk);
 ONELLM_API int onellm_llama_set_graphs(onellm_llama* m, int enabled);
+/* 1: run the context phase one position at a time through the decode kernels (cross-check path);
+ * 0 (default): all prompt tokens at once through the context-phase kernels. */
+ONELLM_API int onellm_llama_set_prefill_by_decode(onellm_llama* m, int enabled);
 
 /* Context phase for `batch` prompts of equal length (host ids [batch, prompt_len]); resets the
  * sequence state.  host_first_ids (may be NULL) receives the first generated token per prompt. */

@@ -223,6 +223,9 @@ class Llama:
     def set_graphs(self, enabled: bool):
         _check(lib().onellm_llama_set_graphs(self._h, C.c_int(1 if enabled else 0)))
 
+    def set_prefill_by_decode(self, enabled: bool):
+        _check(lib().onellm_llama_set_prefill_by_decode(self._h, C.c_int(1 if enabled else 0)))
+
     def prefill(self, ids):
         """ids: int32 numpy [batch, prompt_len]; returns the first sampled id per sequence."""
         import numpy as np

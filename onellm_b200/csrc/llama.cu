@@ -162,6 +162,10 @@ struct Llama {
     long launches = 0;  // kernels enqueued by this model (graph replays count their nodes)
     std::map<long, int> graph_nodes;
     std::map<long, int> warmed;  // keys whose first step already ran outside a capture
+    // context-phase scratch for T prompt tokens, grown on demand (separate from the arena)
+    char* pf_buf = nullptr;
+    size_t pf_tokens = 0;
+    bool prefill_by_decode = false;  // true: run the context phase one position at a time (reference path for tests)
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -374,6 +378,88 @@ static int run_step(Llama& m, int mode, int prompt_len)
     return ONELLM_OK;
 }
 
+// ---- context phase ------------------------------------------------------------------------------
+// All prompt tokens of the batch at once: tensor-core projections (M = batch * prompt_len), the
+// fused QKV bias + RoPE + cache write, causal attention over the cache, then the LM head on the
+// last token of every sequence.  Same arithmetic as running the positions one by one through the
+// decode kernels (which `prefill_by_decode` still does, for cross-checking).
+static int prefill_context(Llama& m, int B, int P)
+{
+    const auto& c = m.c;
+    const int h = c.hidden, D = c.head_size;
+    const size_t T = (size_t)B * P;
+    cudaStream_t st = m.stream;
+    void* sp = (void*)st;
+    // scratch layout for T tokens
+    const size_t per_tok = ((size_t)2 * h + m.qkv_cols + (size_t)m.Hl * D + (size_t)2 * m.Il) * sizeof(__half);
+    if (T > m.pf_tokens) {
+        ONELLM_CUDA(cudaStreamSynchronize(st));
+        if (m.pf_buf) cudaFree(m.pf_buf);
+        m.pf_buf = nullptr;
+        m.pf_tokens = 0;
+        const cudaError_t e = cudaMalloc(&m.pf_buf, T * per_tok + 6 * 256 + (size_t)(2 * c.max_batch + 2) * sizeof(int));
+        ONELLM_REQUIRE(e == cudaSuccess, ONELLM_ERR_CUDA, "llama_prefill: cannot allocate context scratch for %zu tokens: %s", T,
+                       cudaGetErrorString(e));
+        m.pf_tokens = T;
+    }
+    Carver cv{m.pf_buf};
+    __half* y = cv.take<__half>(T * h);
+    __half* res = cv.take<__half>(T * h);
+    __half* qkv = cv.take<__half>(T * m.qkv_cols);
+    __half* attn = cv.take<__half>(T * (size_t)m.Hl * D);
+    __half* act = cv.take<__half>(T * (size_t)m.Il);
+    __half* act2 = cv.take<__half>(T * (size_t)m.Il);
+    int* d_cu = cv.take<int>(c.max_batch + 1);
+    int* d_hist = cv.take<int>(c.max_batch);
+    std::vector<int> cu(B + 1), hist(B, 0);
+    for (int b = 0; b <= B; b++) cu[b] = b * P;
+    ONELLM_CUDA(cudaMemcpyAsync(d_cu, cu.data(), (B + 1) * sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemcpyAsync(d_hist, hist.data(), B * sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaStreamSynchronize(st));  // cu / hist live on this stack frame
+
+    // d_prompt is [B, P] row-major = the packed token order
+    RC(embedding_launch(ONELLM_F16, m.d_prompt, y, res, m.tok_emb, (int)T, h, c.vocab_size, m.d_bad_id, false, st));
+    RC(onellm_rmsnorm(ONELLM_F16, y, m.layers[0].attn_norm, c.rms_eps, (int)T, h, sp));
+    const long cs_b = (long)m.Hkvl * c.max_seq_len * D, cs_h = (long)c.max_seq_len * D, cs_s = D;
+    const float scale = 1.0f / sqrtf((float)D);
+    for (int l = 0; l < c.num_layers; l++) {
+        const LayerW& L = m.layers[l];
+        __half* kc = m.k_cache + (size_t)l * m.cache_layer_elems;
+        __half* vc = m.v_cache + (size_t)l * m.cache_layer_elems;
+        RC(onellm_gemm(ONELLM_F16, y, L.w_qkv, qkv, (int)T, m.qkv_cols, h, ONELLM_W_KN, sp));
+        RC(onellm_qkv_bias_rope_kvcache(ONELLM_F16, qkv, L.b_qkv, d_cu, d_hist, kc, vc, cs_b, cs_h, cs_s, (int)T, B, m.Hl, m.Hkvl,
+                                        D, c.rot_dim, c.rope_base, c.max_seq_len, m.d_bad_id + 1, sp));
+        RC(onellm_context_attn(ONELLM_F16, qkv, m.qkv_cols, kc, vc, cs_b, cs_h, cs_s, d_cu, d_hist, B, P, m.Hl, m.Hkvl, D, scale,
+                               attn, sp));
+        RC(onellm_gemm(ONELLM_F16, attn, L.wo, y, (int)T, h, m.Hl * D, ONELLM_W_KN, sp));
+        RC(tp_allreduce(m, y, T * h));
+        RC(onellm_add_residual_rmsnorm(ONELLM_F16, res, y, L.b_o, L.ffn_norm, c.rms_eps, (int)T, h, sp));
+        if (T <= 64) {
+            RC(onellm_gemm_swiglu(ONELLM_F16, y, L.w1, L.w3, act, (int)T, m.Il, h, sp));
+        } else {
+            RC(onellm_gemm(ONELLM_F16, y, L.w1, act, (int)T, m.Il, h, ONELLM_W_KN, sp));
+            RC(onellm_gemm(ONELLM_F16, y, L.w3, act2, (int)T, m.Il, h, ONELLM_W_KN, sp));
+            RC(swiglu_pair_f16(act, act2, act, T * m.Il, st));
+        }
+        RC(onellm_gemm(ONELLM_F16, act, L.w2, y, (int)T, h, m.Il, ONELLM_W_KN, sp));
+        RC(tp_allreduce(m, y, T * h));
+        const __half* next_gamma = (l + 1 < c.num_layers) ? m.layers[l + 1].attn_norm : m.out_norm;
+        RC(onellm_add_residual_rmsnorm(ONELLM_F16, res, y, nullptr, next_gamma, c.rms_eps, (int)T, h, sp));
+        m.launches += 10;
+    }
+    // last position of every sequence -> LM head, top-K, sampling (seeded with step = P, as the
+    // position-by-position path does)
+    ONELLM_CUDA(cudaMemcpy2DAsync(m.y, (size_t)h * sizeof(__half), y + (size_t)(P - 1) * h, (size_t)P * h * sizeof(__half),
+                                  (size_t)h * sizeof(__half), B, cudaMemcpyDeviceToDevice, st));
+    RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));
+    RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
+    RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
+                          m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, st));
+    m.launches += 5;
+    m.cur_len = P;
+    return ONELLM_OK;
+}
+
 // ---- weight files ------------------------------------------------------------------------------
 // Reads a [rows, cols] tensor (fp32 or fp16 on disk, told apart by the file size), keeps the
 // slice rows [r0, r0+nr) x cols [c0, c0+nc), converts to fp16 and uploads it.
@@ -502,7 +588,16 @@ extern "C" void onellm_llama_destroy(onellm_llama* h)
     if (m->comm && nccl_api().CommDestroy) nccl_api().CommDestroy(m->comm);
     if (m->stream) cudaStreamDestroy(m->stream);
     cudaFree(m->arena);
+    if (m->pf_buf) cudaFree(m->pf_buf);
     delete m;
+}
+
+extern "C" int onellm_llama_set_prefill_by_decode(onellm_llama* h, int enabled)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m, ONELLM_ERR_ARG, "llama_set_prefill_by_decode: null handle");
+    m->prefill_by_decode = enabled != 0;
+    return ONELLM_OK;
 }
 
 extern "C" size_t onellm_llama_device_bytes(const onellm_llama* h)
@@ -661,21 +756,27 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
     m->batch = batch;
     m->graph_prompt_len = prompt_len;
     m->cur_len = 0;
-    const int zero = 0;
+    const int first_step = m->prefill_by_decode ? 0 : prompt_len;  // the step kernels increment before use
     ONELLM_CUDA(cudaMemcpyAsync(m->d_prompt, host_ids, (size_t)batch * prompt_len * sizeof(int), cudaMemcpyHostToDevice, st));
-    ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &zero, sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &first_step, sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemsetAsync(m->d_seqlen, 0, (size_t)batch * sizeof(int), st));
     ONELLM_CUDA(cudaMemsetAsync(m->d_finished, 0, (size_t)batch, st));
-    ONELLM_CUDA(cudaStreamSynchronize(st));  // `zero` lives on this stack frame
-    // context phase, one position at a time through the decode kernels; only the last
-    // position needs the LM head
-    for (int p = 0; p < prompt_len; p++)
-        RC(run_step(*m, MODE_GATHER | (p == prompt_len - 1 ? MODE_HEAD : 0), prompt_len));
+    ONELLM_CUDA(cudaMemsetAsync(m->d_bad_id, 0, 4 * sizeof(int), st));
+    ONELLM_CUDA(cudaStreamSynchronize(st));  // `first_step` lives on this stack frame
+    if (m->prefill_by_decode) {
+        // one position at a time through the decode kernels; only the last position needs the LM head
+        for (int p = 0; p < prompt_len; p++)
+            RC(run_step(*m, MODE_GATHER | (p == prompt_len - 1 ? MODE_HEAD : 0), prompt_len));
+    } else {
+        RC(prefill_context(*m, batch, prompt_len));
+    }
     if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
     ONELLM_CUDA(cudaStreamSynchronize(st));
-    int bad = 0;
-    ONELLM_CUDA(cudaMemcpy(&bad, m->d_bad_id, sizeof(int), cudaMemcpyDeviceToHost));
-    ONELLM_REQUIRE(bad == 0, ONELLM_ERR_ARG, "llama_prefill: token id outside [0, vocab_size)");
+    int bad[2] = {0, 0};
+    ONELLM_CUDA(cudaMemcpy(bad, m->d_bad_id, 2 * sizeof(int), cudaMemcpyDeviceToHost));
+    ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_prefill: token id outside [0, vocab_size)");
+    ONELLM_REQUIRE(bad[1] == 0, ONELLM_ERR_STATE, "llama_prefill: a position beyond max_seq_len was refused by the cache");
+    ONELLM_REQUIRE(onellm_gemm_timeout_flag() <= 0, ONELLM_ERR_CUDA, "llama_prefill: a tensor-core GEMM block timed out");
     return ONELLM_OK;
 }
 

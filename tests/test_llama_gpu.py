@@ -22,13 +22,14 @@ def _make(ob, tmp_path, cfg, seed=0, attn_bias=False, file_dtype=np.float32):
     return m, w
 
 
-@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("graphs,by_decode", [(True, False), (False, False), (True, True)])
 @pytest.mark.parametrize("attn_bias,kv,file_dtype", [(False, 4, np.float32), (True, 2, np.float16)])
-def test_logits_and_greedy_tokens_match_oracle(ob, cuda, orc, tmp_path, graphs, attn_bias, kv, file_dtype):
+def test_logits_and_greedy_tokens_match_oracle(ob, cuda, orc, tmp_path, graphs, by_decode, attn_bias, kv, file_dtype):
     from oracle.llama_ref import LlamaRef
     cfg = dict(CFG, kv_head_num=kv)
     m, w = _make(ob, tmp_path, cfg, seed=kv, attn_bias=attn_bias, file_dtype=file_dtype)
     m.set_graphs(graphs)
+    m.set_prefill_by_decode(by_decode)  # context-phase kernels, or position by position through the decode kernels
     B, P, N = 3, 7, 6
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, cfg["vocab_size"], (B, P)).astype(np.int32)
@@ -98,4 +99,20 @@ def test_random_init_statistics(ob, cuda):
     assert ids.shape == (2, 4)
     lg = m.logits(2)
     assert np.isfinite(lg).all() and lg.std() > 0
+    m.close()
+
+
+def test_context_phase_matches_position_by_position(ob, cuda, tmp_path):
+    """A 100-token prompt (tensor-core GEMMs, M = 300) against the same prompt fed one position at a time."""
+    cfg = dict(CFG, max_seq_len=128)
+    m, w = _make(ob, tmp_path, cfg, seed=9)
+    prompt = np.random.default_rng(2).integers(0, cfg["vocab_size"], (3, 100)).astype(np.int32)
+    m.set_prefill_by_decode(True)
+    a = m.generate(prompt, 6)
+    la = m.logits(3)
+    m.set_prefill_by_decode(False)
+    b = m.generate(prompt, 6)
+    lb = m.logits(3)
+    assert rel_err(lb, la) < 3e-3
+    assert (a == b).mean() > 0.8
     m.close()
