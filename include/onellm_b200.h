@@ -145,6 +145,11 @@ ONELLM_API int onellm_add_residual_rmsnorm(int dtype, void* residual, void* deco
  * ------------------------------------------------------------------------------------- */
 ONELLM_API int onellm_gemm(int dtype, const void* x, const void* W, void* y, int M, int N, int K,
                            int w_layout, void* stream);
+/* The same with an output row stride: row t of y starts at y + t*ldy (ldy >= N).  Lets the gate and
+ * the up projection of the reference's FFN (src/layers/ffn/ffn.cpp:62-64, the shared_out_buf switch
+ * of qkv_linear.cu:37-40) write the two halves of one [T, 2, I] buffer.  F32 only; F16 needs ldy = N. */
+ONELLM_API int onellm_gemm_ld(int dtype, const void* x, const void* W, void* y, long ldy, int M, int N, int K,
+                              int w_layout, void* stream);
 
 /* 1 if a block of the tensor-core GEMM gave up a bounded wait since the last call (the flag is cleared),
  * 0 otherwise, -1 if it cannot be read.  Such a block skips its stores: the output is then incomplete. */
@@ -216,6 +221,66 @@ ONELLM_API int onellm_context_attn(int dtype, const void* q, long q_ld, const vo
                                    long cs_b, long cs_h, long cs_s, const int* cu_seqlens,
                                    const int* history_length, int B, int max_q_len, int H, int Hkv, int D,
                                    float scale, void* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * One-to-one replacements for the nine launchers of the reference's context-attention layer
+ * (src/layers/attention/context_attention.cpp:101-158), for a host that keeps that sequence
+ * as it is.  dtype F32 or F16; all pointers device memory unless named host_*.  New code uses
+ * onellm_qkv_bias_rope_kvcache + onellm_context_attn, which need none of the buffers below.
+ * ------------------------------------------------------------------------------------- */
+/* launchCalPaddingoffset (src/kernels/cal_paddingoffset.h:5-10, cal_paddingoffset.cu:9-46):
+ * cum_seqlens [B+1] exclusive prefix sums of seq_lens [B]; padding_offset [sum] = number of pad
+ * slots in front of each real token in the [B, max_q_len] layout.  host_token_num (may be NULL)
+ * receives the token count; when given, the call synchronises the stream.  1 <= B <= 64. */
+ONELLM_API int onellm_cal_padding_offset(int* padding_offset, int* cum_seqlens, const int* seq_lens, int B,
+                                         int max_q_len, int* host_token_num, void* stream);
+/* launchBuildCausalMasks (src/kernels/build_casual_mask.h:4-9, build_casual_mask.cu:27-60):
+ * mask [B, max_q_len, max_k_len] of 1/0.  attend_history = 0 reproduces the shipped predicate
+ * (build_casual_mask.cu:40-43), which also zeroes the history columns; 1 keeps them. */
+ONELLM_API int onellm_build_causal_mask(int dtype, void* mask, const int* q_lens, const int* k_lens, int max_q_len,
+                                        int max_k_len, int B, int attend_history, void* stream);
+/* launchAddFusedQKVBiasTransposeAndRoPE (src/kernels/qkv_bias_and_RoPE.h:6-14,
+ * qkv_bias_and_RoPE.cu:74-207): packed QKV [num_tokens, H+2*Hkv, D] (+ bias [H+2*Hkv, D], may be
+ * NULL) -> q_buf [B, H, seq_len, D], k_buf / v_buf [B, Hkv, seq_len, D]; interleaved-pair rotation
+ * of q and k at position history_length[b] + local index.  Pad rows are left untouched. */
+ONELLM_API int onellm_qkv_bias_rope_transpose(int dtype, void* q_buf, void* k_buf, void* v_buf, const void* QKV,
+                                              const void* bias, const int* padding_offset,
+                                              const int* history_length, int B, int seq_len, int num_tokens, int H,
+                                              int Hkv, int D, int rotary_dim, float rope_base, void* stream);
+/* launchAppendKVCache (src/kernels/append_to_kvcache.h:20-26, append_to_kvcache.cu:8-114), one
+ * layer, one of K or V: src [B, Hkv, max_q_len, D] -> dst [B, Hkv, max_seq_len, D] at rows
+ * history_length[b] + [0, cur_query_length[b]).  Rows beyond max_seq_len are dropped and
+ * *overflow_flag (device int, may be NULL) is set to 1; the reference writes out of bounds. */
+ONELLM_API int onellm_append_kv_cache(int dtype, void* dst, const void* src, const int* cur_query_length,
+                                      const int* history_length, int B, int Hkv, int max_q_len, int max_seq_len,
+                                      int D, int* overflow_flag, void* stream);
+/* launchTransposeKVCache (src/kernels/transpose_kernel.h:5-11, transpose_kernel.cu:7-88), one
+ * layer: src [B, Hkv, max_seq_len, D] -> dst [B, H, max_k_len, D], query head h reads KV head
+ * h / (H/Hkv), rows [0, context_length[b]); the rest of dst is left untouched. */
+ONELLM_API int onellm_repeat_kv(int dtype, void* dst, const void* src, const int* context_length, int B, int H,
+                                int Hkv, int max_k_len, int max_seq_len, int D, void* stream);
+/* launchLinearStridedBatchGemm (src/kernels/qkv_linear.h:16-20, qkv_linear.cu:67-120):
+ * C[b] = op(A[b]) . op(B[b]) over `batch` row-major matrices, A [m,k] ([k,m] when trans_a),
+ * B [k,n] ([n,k] when trans_b), fp32 accumulation.  A plain tiled kernel: the context phase of
+ * this library never materialises these products. */
+ONELLM_API int onellm_batched_gemm(int dtype, const void* A, const void* Bm, void* Cm, int batch, int m, int n, int k,
+                                   int trans_a, int trans_b, void* stream);
+/* cublasWrapper::Gemm / cublasWrapper::stridedBatchedGemm (src/kernels/cublas_wrapper.h:34-66,
+ * cublas_wrapper.cc:45-147) with the BLAS convention those take: column-major operands,
+ * C[b] (m x n, ldc) = alpha * op(A[b]) . op(B[b]) + beta * C[b], element strides between batches.
+ * batch = 1 is the plain Gemm.  A plain tiled kernel for hosts that call the wrapper directly. */
+ONELLM_API int onellm_gemm_strided_batched(int dtype, int trans_a, int trans_b, int m, int n, int k, const void* A,
+                                           int lda, long stride_a, const void* Bm, int ldb, long stride_b, void* Cm,
+                                           int ldc, long stride_c, int batch, float alpha, float beta, void* stream);
+/* launchScaleMaskAndSoftmax (src/kernels/attn_softmax_kernel.h:5-8, attn_softmax_kernel.cu:45-176):
+ * attn_score [B, H, q_len, k_len] = softmax over the columns where mask [B, q_len, k_len] != 0 of
+ * scale * qk; masked columns and fully masked rows give 0. */
+ONELLM_API int onellm_scale_mask_softmax(int dtype, void* attn_score, const void* qk, const void* mask, int B, int H,
+                                         int q_len, int k_len, float scale, void* stream);
+/* launchTransposeOutRemovePadding (src/kernels/fused_transpose_reshape_remv_pad.h:5-6,
+ * fused_transpose_reshape_remv_pad.cu:5-51): src [B, H, S, D] -> dst [num_tokens, H*D]. */
+ONELLM_API int onellm_transpose_remove_padding(int dtype, void* dst, const void* src, const int* padding_offset,
+                                               int num_tokens, int B, int S, int H, int D, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Row-wise top-K of logits [rows, vocab] (F32 or F16), values sorted descending, ties to

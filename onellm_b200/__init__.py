@@ -157,6 +157,53 @@ def context_attn(dtype, q, q_ld, k_cache, v_cache, cs_b, cs_h, cs_s, cu_seqlens,
                                      _stream(stream)))
 
 
+def cal_padding_offset(padding_offset, cum_seqlens, seq_lens, B, max_q_len, want_token_num=True, stream=None):
+    n = C.c_int(0)
+    _check(lib().onellm_cal_padding_offset(_p(padding_offset), _p(cum_seqlens), _p(seq_lens), C.c_int(B), C.c_int(max_q_len),
+                                           C.byref(n) if want_token_num else None, _stream(stream)))
+    return n.value if want_token_num else None
+
+
+def build_causal_mask(dtype, mask, q_lens, k_lens, max_q_len, max_k_len, B, attend_history=False, stream=None):
+    _check(lib().onellm_build_causal_mask(C.c_int(dtype), _p(mask), _p(q_lens), _p(k_lens), C.c_int(max_q_len),
+                                          C.c_int(max_k_len), C.c_int(B), C.c_int(1 if attend_history else 0), _stream(stream)))
+
+
+def qkv_bias_rope_transpose(dtype, q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, B, seq_len, num_tokens,
+                            H, Hkv, D, rot_dim, rope_base, stream=None):
+    _check(lib().onellm_qkv_bias_rope_transpose(C.c_int(dtype), _p(q_buf), _p(k_buf), _p(v_buf), _p(QKV), _p(bias),
+                                                _p(padding_offset), _p(history_length), C.c_int(B), C.c_int(seq_len),
+                                                C.c_int(num_tokens), C.c_int(H), C.c_int(Hkv), C.c_int(D), C.c_int(rot_dim),
+                                                C.c_float(rope_base), _stream(stream)))
+
+
+def append_kv_cache(dtype, dst, src, cur_query_length, history_length, B, Hkv, max_q_len, max_seq_len, D,
+                    overflow_flag=None, stream=None):
+    _check(lib().onellm_append_kv_cache(C.c_int(dtype), _p(dst), _p(src), _p(cur_query_length), _p(history_length),
+                                        C.c_int(B), C.c_int(Hkv), C.c_int(max_q_len), C.c_int(max_seq_len), C.c_int(D),
+                                        _p(overflow_flag), _stream(stream)))
+
+
+def repeat_kv(dtype, dst, src, context_length, B, H, Hkv, max_k_len, max_seq_len, D, stream=None):
+    _check(lib().onellm_repeat_kv(C.c_int(dtype), _p(dst), _p(src), _p(context_length), C.c_int(B), C.c_int(H),
+                                  C.c_int(Hkv), C.c_int(max_k_len), C.c_int(max_seq_len), C.c_int(D), _stream(stream)))
+
+
+def batched_gemm(dtype, A, Bm, Cm, batch, m, n, k, trans_a=False, trans_b=False, stream=None):
+    _check(lib().onellm_batched_gemm(C.c_int(dtype), _p(A), _p(Bm), _p(Cm), C.c_int(batch), C.c_int(m), C.c_int(n),
+                                     C.c_int(k), C.c_int(1 if trans_a else 0), C.c_int(1 if trans_b else 0), _stream(stream)))
+
+
+def scale_mask_softmax(dtype, attn_score, qk, mask, B, H, q_len, k_len, scale, stream=None):
+    _check(lib().onellm_scale_mask_softmax(C.c_int(dtype), _p(attn_score), _p(qk), _p(mask), C.c_int(B), C.c_int(H),
+                                           C.c_int(q_len), C.c_int(k_len), C.c_float(scale), _stream(stream)))
+
+
+def transpose_remove_padding(dtype, dst, src, padding_offset, num_tokens, B, S, H, D, stream=None):
+    _check(lib().onellm_transpose_remove_padding(C.c_int(dtype), _p(dst), _p(src), _p(padding_offset), C.c_int(num_tokens),
+                                                 C.c_int(B), C.c_int(S), C.c_int(H), C.c_int(D), _stream(stream)))
+
+
 def topk(dtype, logits, rows, vocab, K, out_val, out_id, global_ids=False, stream=None):
     _check(lib().onellm_topk(C.c_int(dtype), _p(logits), C.c_int(rows), C.c_int(vocab), C.c_int(K),
                              _p(out_val), _p(out_id), C.c_int(1 if global_ids else 0), _stream(stream)))

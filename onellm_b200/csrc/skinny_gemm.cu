@@ -87,7 +87,7 @@ skinny_nk_kernel(const __half* __restrict__ x, const __half* __restrict__ W, __h
 // per thread.  Correctness path for fp32 callers, not a tuned kernel.
 template <bool W_NK>
 __global__ void __launch_bounds__(256)
-sgemm_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ y, int M, int N, int K)
+sgemm_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __restrict__ y, int M, int N, int K, long ldy)
 {
     __shared__ float xs[16][64 + 1];
     __shared__ float ws[16][64 + 1];
@@ -129,7 +129,7 @@ sgemm_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-            if (m < M && n < N) y[(size_t)m * N + n] = acc[i][j];
+            if (m < M && n < N) y[(size_t)m * ldy + n] = acc[i][j];
         }
 }
 
@@ -213,11 +213,11 @@ int gemm_f16_skinny(const __half* x, const __half* W, __half* y, int M, int N, i
 
 using namespace onellm;
 
-extern "C" int onellm_gemm(int dtype, const void* x, const void* W, void* y, int M, int N, int K, int w_layout,
-                           void* stream)
+extern "C" int onellm_gemm_ld(int dtype, const void* x, const void* W, void* y, long ldy, int M, int N, int K, int w_layout,
+                              void* stream)
 {
     ONELLM_REQUIRE(x && W && y, ONELLM_ERR_ARG, "gemm: null pointer");
-    ONELLM_REQUIRE(M >= 0 && N > 0 && K > 0, ONELLM_ERR_ARG, "gemm: bad size M=%d N=%d K=%d", M, N, K);
+    ONELLM_REQUIRE(M >= 0 && N > 0 && K > 0 && ldy >= N, ONELLM_ERR_ARG, "gemm: bad size M=%d N=%d K=%d ldy=%ld", M, N, K, ldy);
     ONELLM_REQUIRE(w_layout == ONELLM_W_KN || w_layout == ONELLM_W_NK, ONELLM_ERR_ARG, "gemm: bad w_layout %d",
                    w_layout);
     if (M == 0) return ONELLM_OK;
@@ -226,13 +226,14 @@ extern "C" int onellm_gemm(int dtype, const void* x, const void* W, void* y, int
         const dim3 grid((N + 63) / 64, (M + 63) / 64);
         ONELLM_REQUIRE(grid.y <= 65535, ONELLM_ERR_UNSUPPORTED, "gemm: M too large for the fp32 path");
         if (w_layout == ONELLM_W_NK)
-            sgemm_kernel<true><<<grid, 256, 0, st>>>((const float*)x, (const float*)W, (float*)y, M, N, K);
+            sgemm_kernel<true><<<grid, 256, 0, st>>>((const float*)x, (const float*)W, (float*)y, M, N, K, ldy);
         else
-            sgemm_kernel<false><<<grid, 256, 0, st>>>((const float*)x, (const float*)W, (float*)y, M, N, K);
+            sgemm_kernel<false><<<grid, 256, 0, st>>>((const float*)x, (const float*)W, (float*)y, M, N, K, ldy);
         ONELLM_CHECK_LAUNCH();
         return ONELLM_OK;
     }
     ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "gemm: dtype %d", dtype);
+    ONELLM_REQUIRE(ldy == N, ONELLM_ERR_UNSUPPORTED, "gemm: the F16 kernels write dense rows (ldy must equal N)");
     ONELLM_REQUIRE(aligned16(x) && aligned16(W) && aligned16(y), ONELLM_ERR_ARG,
                    "gemm: pointers must be 16-byte aligned");
     const __half* xh = (const __half*)x;
@@ -240,6 +241,12 @@ extern "C" int onellm_gemm(int dtype, const void* x, const void* W, void* y, int
     __half* yh = (__half*)y;
     if (M > 64) return gemm_f16_large(xh, Wh, yh, M, N, K, w_layout, st);
     return gemm_f16_skinny(xh, Wh, yh, M, N, K, w_layout, st);
+}
+
+extern "C" int onellm_gemm(int dtype, const void* x, const void* W, void* y, int M, int N, int K, int w_layout,
+                           void* stream)
+{
+    return onellm_gemm_ld(dtype, x, W, y, N, M, N, K, w_layout, stream);
 }
 
 extern "C" int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, const void* Wu, void* out, int M,

@@ -390,13 +390,6 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
             best_nst = 3;
         }
     }
-    if (const char* e = getenv("ONELLM_DEV_STAGED_PLAN")) {  // development sweep: "ks,nst"
-        int ks = 0, nst = 0;
-        if (sscanf(e, "%d,%d", &ks, &nst) == 2 && ks >= 1 && ks <= 8 && nst >= 3) {
-            best_ks = ks;
-            best_nst = nst;
-        }
-    }
     const int per_block_final = (total_stages + best_ks - 1) / best_ks;
     const size_t xn_final = FUSED ? (size_t)8 * MB * (per_block_final * kKC + 8) * sizeof(__half) : 0;
     const size_t smem_final = std::max(stage * best_nst, red) + xn_final;
