@@ -136,6 +136,22 @@ ONELLM_API int onellm_add_residual_rmsnorm(int dtype, void* residual, void* deco
                                            int num_tokens, int hidden, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * A decoder sub-block without norm kernels (F16, M <= 64, [K,N] weights).  No single counterpart
+ * in the reference: it is launchFusedAddBiasResidualRMSNorm + launchLinearGemm (+ launchAct)
+ * of src/layers/decoder/self_decoder.cpp:47-73 regrouped around the projections:
+ *
+ *   t = x . W                         (Wu == NULL)      t = silu(x . W) * (x . Wu)   (Wu != NULL)
+ *   rms_eps >= 0:  both products are scaled per token by rsqrt(mean_K(x^2) + rms_eps) first, which
+ *                  makes them the projection of RMSNorm(x) if the norm's gamma[k] has been multiplied
+ *                  into row k of W (and Wu) beforehand; rms_eps < 0: no scaling
+ *   y = t                             (resid == NULL)   y = resid + bias + t         (bias may be NULL)
+ *
+ * resid may be y itself (residual stream updated in place); y must not alias x.
+ * ------------------------------------------------------------------------------------- */
+ONELLM_API int onellm_gemm_fused(int dtype, const void* x, const void* W, const void* Wu, void* y, int M, int N,
+                                 int K, float rms_eps, const void* resid, const void* bias, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Projection y[M,N] = x[M,K] . W  (fp32 accumulation, no bias).
  * Replaces launchLinearGemm + cublasWrapper::Gemm
  * (src/kernels/qkv_linear.h:9-14, qkv_linear.cu:8-65, cublas_wrapper.cc:45-90).

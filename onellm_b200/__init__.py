@@ -119,6 +119,11 @@ def gemm(dtype, x, W, y, M, N, K, w_layout=W_KN, stream=None):
                              C.c_int(w_layout), _stream(stream)))
 
 
+def gemm_fused(dtype, x, W, Wu, y, M, N, K, rms_eps=-1.0, resid=None, bias=None, stream=None):
+    _check(lib().onellm_gemm_fused(C.c_int(dtype), _p(x), _p(W), _p(Wu), _p(y), C.c_int(M), C.c_int(N), C.c_int(K),
+                                   C.c_float(rms_eps), _p(resid), _p(bias), _stream(stream)))
+
+
 def gemm_swiglu(dtype, x, Wg, Wu, out, M, I, K, stream=None):
     _check(lib().onellm_gemm_swiglu(C.c_int(dtype), _p(x), _p(Wg), _p(Wu), _p(out), C.c_int(M), C.c_int(I),
                                     C.c_int(K), _stream(stream)))

@@ -23,6 +23,7 @@ namespace onellm {
 
 constexpr int kTcBM = 128, kTcBN = 128, kTcBK = 64;
 constexpr int kTcStages = 3;
+constexpr int kTcBand = 16;  // row tiles per band of the tile order
 constexpr int kTcThreads = 128;
 constexpr int kTcATile = kTcBM * kTcBK * 2;        // 16 KB: 128 rows x 128 bytes
 constexpr int kTcBTile = kTcBN * kTcBK * 2;        // 16 KB: [K,N] two boxes of 64 k-rows x 128 bytes; [N,K] 128 rows x 128 bytes
@@ -109,7 +110,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 1);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcStages), accum_bar = smem_u32(bars + 2 * kTcStages);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kTcBN, m0 = blockIdx.y * kTcBM;
+    // Tile order: the linear block index walks down a band of kTcBand row tiles, then moves one column
+    // tile to the right, so the blocks resident at one time (about two per SM) cover a near-square patch
+    // of the output and share their A row blocks and B column blocks in L2.  (Row-major order made every
+    // wave touch all column tiles of B: operands were read from DRAM seven times over.)
+    const int tiles_m = (M + kTcBM - 1) / kTcBM, tiles_n = (N + kTcBN - 1) / kTcBN;
+    int tile_m, tile_n;
+    {
+        const int per_band = kTcBand * tiles_n;
+        const int band = blockIdx.x / per_band, in_band = blockIdx.x % per_band;
+        const int band_rows = min(kTcBand, tiles_m - band * kTcBand);
+        tile_m = band * kTcBand + in_band % band_rows;
+        tile_n = in_band / band_rows;
+    }
+    const int n0 = tile_n * kTcBN, m0 = tile_m * kTcBM;
     const int k_steps = (K + kTcBK - 1) / kTcBK;
 
     if (threadIdx.x == 0) {
@@ -266,8 +280,9 @@ int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, in
             attr_set[nk] = true;
         }
     }
-    const dim3 grid((N + kTcBN - 1) / kTcBN, (M + kTcBM - 1) / kTcBM);
-    ONELLM_REQUIRE(grid.y <= 65535, ONELLM_ERR_UNSUPPORTED, "gemm: M too large");
+    const long tiles = (long)((N + kTcBN - 1) / kTcBN) * ((M + kTcBM - 1) / kTcBM);
+    ONELLM_REQUIRE(tiles <= 0x7fffffffL, ONELLM_ERR_UNSUPPORTED, "gemm: too many tiles");
+    const dim3 grid((unsigned)tiles);
     if (nk)
         ONELLM_CUDA(launch_pdl(gemm_tc_kernel<true>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, y, M, N, K));
     else

@@ -114,6 +114,15 @@ __global__ void init_normal_kernel(__half* __restrict__ w, size_t rows, size_t c
     }
 }
 
+// W[k, :] *= gamma[k]: the RMSNorm in front of a projection, moved into the projection's weights
+// (RMSNorm(x) . W = rsqrt(mean(x^2) + eps) * (x . diag(gamma) W)), product rounded once to fp16.
+__global__ void fold_gamma_kernel(__half* __restrict__ w, const __half* __restrict__ gamma, size_t rows, size_t cols)
+{
+    const size_t n = rows * cols;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        w[i] = __float2half_rn(__half2float(w[i]) * __half2float(gamma[i / cols]));
+}
+
 __global__ void fill_half_kernel(__half* w, size_t n, float v)
 {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -237,7 +246,8 @@ int embedding_launch(int dtype, const int* ids, void* out, void* out2, const voi
 // sampling.cu
 int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, float temperature, int rng_step,
                        const int* rng_step_dev, int vocab_size, int end_id, int literal_walk, int* output_id,
-                       int* seqlen, unsigned char* finished, float* u_out, int* output_id2, cudaStream_t st);
+                       int* seqlen, unsigned char* finished, float* u_out, int* output_id2, bool early_seed,
+                       cudaStream_t st);
 
 #define RC(call)              \
     do {                      \
@@ -288,10 +298,30 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
                                   cs_b, cs_h, cs_s, B, m.Hl, m.Hkvl, D, step_bound, m.d_step, step_bound - 1, c.rot_dim,
                                   c.rope_base, scale, m.attn, (long)m.Hl * D, m.attn_ws, m.attn_ws_bytes, sp);
     };
-    {
-        // (onellm_add_residual_rmsnorm_gemm folds each norm into the projection after it; measured on
-        // B200 it is no faster than the two launches below, because every block of the projection
-        // repeats the row statistics, so the model keeps the separate norm kernels)
+    const __half* head_in = m.y;
+    if (c.tp_size == 1) {
+        // Five kernels per layer, no norm kernels: the residual stream lives in m.res, each projection
+        // that follows a norm reads it raw and scales by rsqrt(mean(x^2) + eps) on the way out (the
+        // norm's gamma is already inside its weights), o_proj and down_proj add their result to it.
+        RC(embedding_launch(ONELLM_F16, m.d_ids, m.res, nullptr, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
+        m.launches += 2;
+        for (int l = 0; l < c.num_layers; l++) {
+            const LayerW& L = m.layers[l];
+            RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w_qkv, nullptr, m.qkv, B, m.qkv_cols, h, c.rms_eps, nullptr, nullptr, sp));
+            RC(attention(l));
+            RC(onellm_gemm_fused(ONELLM_F16, m.attn, L.wo, nullptr, m.res, B, h, m.Hl * D, -1.f, m.res, L.b_o, sp));
+            RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w1, L.w3, m.act, B, m.Il, h, c.rms_eps, nullptr, nullptr, sp));
+            RC(onellm_gemm_fused(ONELLM_F16, m.act, L.w2, nullptr, m.res, B, h, m.Il, -1.f, m.res, nullptr, sp));
+            m.launches += 6;  // qkv, attention + combine, o, gate/up, down
+        }
+        if (mode & MODE_HEAD) {
+            RC(onellm_rmsnorm(ONELLM_F16, m.res, m.out_norm, c.rms_eps, B, h, sp));  // in place: the stream ends here
+            m.launches += 1;
+        }
+        head_in = m.res;
+    } else {
+        // tensor parallel: partial sums of o_proj and down_proj are all-reduced before the residual add,
+        // so the norm kernels stay (their per-layer gamma is all ones after finalize_weights)
         RC(embedding_launch(ONELLM_F16, m.d_ids, m.y, m.res, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
         RC(onellm_rmsnorm(ONELLM_F16, m.y, m.layers[0].attn_norm, c.rms_eps, B, h, sp));
         m.launches += 3;
@@ -311,10 +341,10 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         }
     }
     if (mode & MODE_HEAD) {
-        RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));
+        RC(onellm_gemm(ONELLM_F16, head_in, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));
         RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
         RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size,
-                              c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, st));
+                              c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
         m.launches += 3;
     }
     ONELLM_CHECK_LAUNCH();
@@ -454,7 +484,7 @@ static int prefill_context(Llama& m, int B, int P)
     RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));
     RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
     RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
-                          m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, st));
+                          m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
     m.launches += 5;
     m.cur_len = P;
     return ONELLM_OK;
@@ -633,6 +663,29 @@ extern "C" int onellm_llama_init_comm(onellm_llama* h, const void* id128)
     return ONELLM_OK;
 }
 
+// After the weights are in place: every layer's two norm vectors are multiplied into the rows of the
+// projections that follow them (QKV; gate and up) and replaced by ones.  The decode step then needs no
+// norm kernel between projections (onellm_gemm_fused scales by the row statistics on the way out), and
+// the paths that still run the norm kernels (context phase, tensor parallel) compute x / rms(x) with the
+// all-ones vectors in front of the same folded weights.  The final norm in front of the LM head stays.
+static int finalize_weights(Llama& m)
+{
+    const auto& c = m.c;
+    cudaStream_t st = m.stream;
+    const size_t hd = c.hidden;
+    for (auto& L : m.layers) {
+        fold_gamma_kernel<<<blocks_for(hd * m.qkv_cols), 256, 0, st>>>(L.w_qkv, L.attn_norm, hd, (size_t)m.qkv_cols);
+        fold_gamma_kernel<<<blocks_for(hd * m.Il), 256, 0, st>>>(L.w1, L.ffn_norm, hd, (size_t)m.Il);
+        fold_gamma_kernel<<<blocks_for(hd * m.Il), 256, 0, st>>>(L.w3, L.ffn_norm, hd, (size_t)m.Il);
+        fill_half_kernel<<<blocks_for(hd), 256, 0, st>>>(L.attn_norm, hd, 1.0f);
+        fill_half_kernel<<<blocks_for(hd), 256, 0, st>>>(L.ffn_norm, hd, 1.0f);
+    }
+    ONELLM_CHECK_LAUNCH();
+    ONELLM_CUDA(cudaStreamSynchronize(st));
+    m.weights_ready = true;
+    return ONELLM_OK;
+}
+
 extern "C" int onellm_llama_init_random(onellm_llama* h, uint64_t seed, float std)
 {
     Llama* m = reinterpret_cast<Llama*>(h);
@@ -682,9 +735,7 @@ extern "C" int onellm_llama_init_random(onellm_llama* h, uint64_t seed, float st
     normal(m->out_w, V, hd, hd, 0, 0, 1000002);
     ones(m->out_norm, hd);
     ONELLM_CHECK_LAUNCH();
-    ONELLM_CUDA(cudaStreamSynchronize(st));
-    m->weights_ready = true;
-    return ONELLM_OK;
+    return finalize_weights(*m);
 }
 
 extern "C" int onellm_llama_load_weights(onellm_llama* h, const char* weight_path)
@@ -713,8 +764,7 @@ extern "C" int onellm_llama_load_weights(onellm_llama* h, const char* weight_pat
             RC(load_slice(lp + ".attention.wo.bias", 1, hd, 0, 1, 0, hd, L.b_o));
         }
     }
-    m->weights_ready = true;
-    return ONELLM_OK;
+    return finalize_weights(*m);
 }
 
 extern "C" int onellm_llama_set_sampling(onellm_llama* h, int top_k, float temperature, int literal_walk)

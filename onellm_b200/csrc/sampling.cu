@@ -5,10 +5,14 @@
 // to 1 <= K <= 64 with a defined order for ties (lower column first).  Sampling restates
 // SamplingKernel (src/kernels/topK_sampling.cu:6-41) with the same cuRAND call sequence.
 //
-// Top-K is a radix select, one thread block per row: four 8-bit histogram passes over an
-// order-preserving integer image of the logits find the K-th largest key, then everything
-// above it plus the lowest-indexed ties are gathered and rank-sorted.  The row (128 KB at
-// vocab 32000) stays in L2 between passes.
+// Top-K is a radix select, one thread block per row: 8-bit histogram passes over an
+// order-preserving integer image of the logits find the K-th largest key (two passes for fp16
+// logits, whose image has 16 bits, four for fp32), then everything above it plus the
+// lowest-indexed ties are gathered and rank-sorted.  Rows of up to 32768 logits are read once:
+// every thread keeps its 32 consecutive keys in registers for all passes; histogram updates are
+// aggregated per warp before they reach shared memory (logits share their leading bits, so
+// plain atomics would serialise on a handful of bins).  Longer rows re-read the logits from L2
+// in every pass.
 #include <curand_kernel.h>
 #include <math.h>
 
@@ -148,24 +152,211 @@ topk_kernel(const T* __restrict__ logits, int vocab, int K, float* __restrict__ 
     }
 }
 
+
+template <typename T>
+__device__ __forceinline__ uint32_t logit_key(T v);
+template <>
+__device__ __forceinline__ uint32_t logit_key<float>(float v) { return float_key(v); }
+template <>
+__device__ __forceinline__ uint32_t logit_key<__half>(__half v)
+{
+    // 16-bit image in the upper half of the key: same order as the float image, two radix passes
+    const uint32_t u = __half_as_ushort(v);
+    if ((u & 0x7fffu) > 0x7c00u) return 0u;  // NaN
+    return ((u & 0x8000u) ? (~u & 0xffffu) : (u | 0x8000u)) << 16;
+}
+template <typename T>
+__device__ __forceinline__ float key_value(uint32_t k);
+template <>
+__device__ __forceinline__ float key_value<float>(uint32_t k) { return key_float(k); }
+template <>
+__device__ __forceinline__ float key_value<__half>(uint32_t k)
+{
+    const uint32_t k16 = k >> 16;
+    const uint32_t u = (k16 & 0x8000u) ? (k16 & 0x7fffu) : (~k16 & 0xffffu);
+    return __half2float(__ushort_as_half((unsigned short)u));
+}
+
+constexpr int kTopkPer = 32;  // keys per thread held in registers
+
+// warp-aggregated histogram update: lanes with the same digit elect one to add their count
+__device__ __forceinline__ void hist_add(int* hist, bool pred, uint32_t digit)
+{
+    const unsigned act = __ballot_sync(0xffffffffu, pred);
+    if (pred) {
+        const unsigned peers = __match_any_sync(act, digit);
+        if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[digit], __popc(peers));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kTopkThreads)
+topk_reg_kernel(const T* __restrict__ logits, int vocab, int K, float* __restrict__ out_val, int* __restrict__ out_id,
+                int global_ids)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const T* x = logits + (size_t)row * vocab;
+    __shared__ int hist[256];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_need, s_count;
+    __shared__ int warp_tot[kTopkThreads / 32];
+    __shared__ uint32_t cand_key[kMaxK];
+    __shared__ int cand_id[kMaxK];
+    constexpr int kPasses = sizeof(T) == 2 ? 2 : 4;
+
+    // thread t owns columns [t*32, t*32 + 32): a contiguous slice, so ranks inside a tie follow the columns
+    const int c0 = threadIdx.x * kTopkPer;
+    const int n_mine = max(0, min(kTopkPer, vocab - c0));
+    uint32_t key[kTopkPer];
+    constexpr int VEC = 16 / sizeof(T);
+    if (n_mine == kTopkPer && ((reinterpret_cast<uintptr_t>(x + c0) & 15u) == 0)) {
+#pragma unroll
+        for (int j = 0; j < kTopkPer; j += VEC) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + c0 + j);
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int q = 0; q < VEC; q++) key[j + q] = logit_key<T>(e[q]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < kTopkPer; j++) key[j] = j < n_mine ? logit_key<T>(x[c0 + j]) : 0u;
+    }
+    if (threadIdx.x == 0) {
+        s_prefix = 0u;
+        s_need = K;
+        s_count = 0;
+    }
+    __syncthreads();
+
+    // 1. K-th largest key, 8 bits at a time from the top
+#pragma unroll 1
+    for (int pass = 0; pass < kPasses; pass++) {
+        const int shift = 24 - 8 * pass;
+        const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = threadIdx.x; i < 256; i += kTopkThreads) hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+#pragma unroll
+        for (int j = 0; j < kTopkPer; j++) hist_add(hist, j < n_mine && (key[j] & mask) == prefix, (key[j] >> shift) & 255u);
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            // warp 0 walks the 256 bins from the top: lane l owns bins 255-8l .. 248-8l
+            int mine = 0;
+#pragma unroll
+            for (int q = 0; q < 8; q++) mine += hist[255 - 8 * (int)threadIdx.x - q];
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if ((int)threadIdx.x >= o) incl += v;
+            }
+            const int need = s_need;
+            const int before = incl - mine;  // keys in bins above this lane's
+            // the lane whose bins contain the need-th key; bin 0 takes whatever is left
+            const bool here = before < need && (incl >= need || threadIdx.x == 31);
+            if (here) {
+                int left = need - before, b = 255 - 8 * (int)threadIdx.x;
+                for (int q = 0; q < 8; q++, b--) {
+                    if (hist[b] >= left || b == 0) break;
+                    left -= hist[b];
+                }
+                s_prefix = prefix | ((uint32_t)b << shift);
+                s_need = left;
+            }
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = s_prefix;
+    const int need_ties = s_need;
+
+    // 2. gather: everything above the K-th key (any order), then the lowest-indexed ties
+    int ties = 0;
+#pragma unroll
+    for (int j = 0; j < kTopkPer; j++) {
+        if (j < n_mine && key[j] > kth) {
+            const int pos = atomicAdd(&s_count, 1);
+            cand_key[pos] = key[j];
+            cand_id[pos] = c0 + j;
+        }
+        ties += (j < n_mine && key[j] == kth);
+    }
+    __syncthreads();
+    const int n_above = s_count;  // == K - need_ties
+    {
+        int incl = ties;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if ((threadIdx.x & 31) >= o) incl += v;
+        }
+        if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            const int v = warp_tot[threadIdx.x];
+            int inc = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, inc, o);
+                if ((int)threadIdx.x >= o) inc += u;
+            }
+            warp_tot[threadIdx.x] = inc - v;  // exclusive
+        }
+        __syncthreads();
+        int rank = warp_tot[threadIdx.x >> 5] + incl - ties;
+        if (ties > 0 && rank < need_ties) {
+#pragma unroll
+            for (int j = 0; j < kTopkPer; j++) {
+                if (j < n_mine && key[j] == kth && rank < need_ties) {
+                    cand_key[n_above + rank] = kth;
+                    cand_id[n_above + rank] = c0 + j;
+                    rank++;
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // 3. rank sort: larger key first, lower column first among equals
+    if (threadIdx.x < K) {
+        const uint32_t k = cand_key[threadIdx.x];
+        const int id = cand_id[threadIdx.x];
+        int r = 0;
+        for (int j = 0; j < K; j++) r += (cand_key[j] > k) || (cand_key[j] == k && cand_id[j] < id);
+        out_val[(size_t)row * K + r] = (k == 0u) ? -INFINITY : key_value<T>(k);
+        out_id[(size_t)row * K + r] = global_ids ? row * vocab + id : id;
+    }
+}
+
 __global__ void sample_kernel(const int* __restrict__ topk_id, const float* __restrict__ topk_val, int K,
                               float temperature, int rng_step, const int* __restrict__ rng_step_dev,
                               int vocab_size, int end_id, int literal_walk, int* __restrict__ output_id, int* __restrict__ seqlen,
                               unsigned char* __restrict__ finished, float* __restrict__ u_out,
-                              int* __restrict__ output_id2)
+                              int* __restrict__ output_id2, int early_seed)
 {
     pdl_launch_dependents();
-    pdl_wait();
     const int b = blockIdx.x;
+    // The draw depends on (step, row) only, and seeding the generator (a sequence skip-ahead) is by far
+    // the longest part of this kernel.  early_seed: do it before waiting for the candidates; the caller
+    // vouches that *rng_step_dev was written by work that completed long before (the model's step
+    // counter is advanced by the first kernel of a step, and the layer projections between it and this
+    // kernel release their dependents only after passing their own griddepcontrol.wait).
+    float u = 0.f;
+    auto draw = [&]() {
+        curandState_t state;
+        const int seed = rng_step_dev ? *rng_step_dev : rng_step;
+        curand_init((unsigned long long)seed, (unsigned long long)b, 0ULL, &state);
+        u = curand_uniform(&state);
+    };
+    if (early_seed && threadIdx.x == 0) draw();
+    pdl_wait();
     if (threadIdx.x != 0) return;
+    if (!early_seed) draw();
     const float* v = topk_val + (size_t)b * K;
     const float v0 = v[0];
     float sum = 0.f;
     for (int i = 0; i < K; i++) sum += expf((v[i] - v0) / temperature);
-    curandState_t state;
-    const int seed = rng_step_dev ? *rng_step_dev : rng_step;
-    curand_init((unsigned long long)seed, (unsigned long long)b, 0ULL, &state);
-    const float u = curand_uniform(&state);
     if (u_out) u_out[b] = u;
     float thr = u * sum;
     int pick = K - 1;
@@ -198,12 +389,13 @@ extern "C" int onellm_topk(int dtype, const void* logits, int rows, int vocab, i
                    kMaxK);
     if (rows == 0) return ONELLM_OK;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const bool in_regs = vocab <= kTopkPer * kTopkThreads;
     if (dtype == ONELLM_F16)
-        ONELLM_CUDA(launch_pdl(topk_kernel<__half>, dim3(rows), dim3(kTopkThreads), 0, st, (const __half*)logits, vocab, K,
-                               out_val, out_id, global_ids));
+        ONELLM_CUDA(launch_pdl(in_regs ? topk_reg_kernel<__half> : topk_kernel<__half>, dim3(rows), dim3(kTopkThreads), 0, st,
+                               (const __half*)logits, vocab, K, out_val, out_id, global_ids));
     else if (dtype == ONELLM_F32)
-        ONELLM_CUDA(launch_pdl(topk_kernel<float>, dim3(rows), dim3(kTopkThreads), 0, st, (const float*)logits, vocab, K,
-                               out_val, out_id, global_ids));
+        ONELLM_CUDA(launch_pdl(in_regs ? topk_reg_kernel<float> : topk_kernel<float>, dim3(rows), dim3(kTopkThreads), 0, st,
+                               (const float*)logits, vocab, K, out_val, out_id, global_ids));
     else
         ONELLM_REQUIRE(false, ONELLM_ERR_UNSUPPORTED, "topk: dtype %d", dtype);
     ONELLM_CHECK_LAUNCH();
@@ -215,7 +407,8 @@ namespace onellm {
 // copy of the sampled ids (the next step's input buffer).
 int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, float temperature, int rng_step,
                        const int* rng_step_dev, int vocab_size, int end_id, int literal_walk, int* output_id,
-                       int* seqlen, unsigned char* finished, float* u_out, int* output_id2, cudaStream_t st)
+                       int* seqlen, unsigned char* finished, float* u_out, int* output_id2, bool early_seed,
+                       cudaStream_t st)
 {
     ONELLM_REQUIRE(topk_id && topk_val && output_id, ONELLM_ERR_ARG, "topk_sample: null pointer");
     ONELLM_REQUIRE(B >= 0 && K >= 1 && vocab_size > 0 && temperature > 0.f, ONELLM_ERR_ARG,
@@ -225,7 +418,7 @@ int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, 
     if (B == 0) return ONELLM_OK;
     ONELLM_CUDA(launch_pdl(sample_kernel, dim3(B), dim3(32), 0, st, topk_id, topk_val, K, temperature, rng_step,
                            rng_step_dev, vocab_size, end_id, literal_walk, output_id, seqlen, finished, u_out,
-                           output_id2));
+                           output_id2, early_seed ? 1 : 0));
     return ONELLM_OK;
 }
 }  // namespace onellm
@@ -236,6 +429,6 @@ extern "C" int onellm_topk_sample(const int* topk_id, const float* topk_val, int
                                   float* u_out, void* stream)
 {
     return topk_sample_launch(topk_id, topk_val, B, K, temperature, rng_step, rng_step_dev, vocab_size, end_id,
-                              literal_walk, output_id, seqlen, finished, u_out, nullptr,
+                              literal_walk, output_id, seqlen, finished, u_out, nullptr, /*early_seed=*/false,
                               reinterpret_cast<cudaStream_t>(stream));
 }

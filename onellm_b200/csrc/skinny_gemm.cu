@@ -135,12 +135,13 @@ sgemm_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __
 
 // skinny_gemm_staged.cu
 cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
-                                      int K, bool dual, cudaStream_t st);
+                                      int K, bool dual, cudaStream_t st, const __half* resid, const __half* bias,
+                                      float rms_eps);
 
 static cudaError_t skinny_kn_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
                                       int K, bool dual, cudaStream_t st)
 {
-    return skinny_kn_staged_dispatch(x, W0, W1, y, M, N, K, dual, st);
+    return skinny_kn_staged_dispatch(x, W0, W1, y, M, N, K, dual, st, nullptr, nullptr, -1.f);
 }
 
 template <int MB, int UK>
@@ -247,6 +248,25 @@ extern "C" int onellm_gemm(int dtype, const void* x, const void* W, void* y, int
                            void* stream)
 {
     return onellm_gemm_ld(dtype, x, W, y, N, M, N, K, w_layout, stream);
+}
+
+extern "C" int onellm_gemm_fused(int dtype, const void* x, const void* W, const void* Wu, void* y, int M, int N, int K,
+                                 float rms_eps, const void* resid, const void* bias, void* stream)
+{
+    ONELLM_REQUIRE(x && W && y, ONELLM_ERR_ARG, "gemm_fused: null pointer");
+    ONELLM_REQUIRE(M >= 0 && N > 0 && K > 0, ONELLM_ERR_ARG, "gemm_fused: bad size");
+    ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "gemm_fused: only F16 is implemented");
+    ONELLM_REQUIRE(M <= 64, ONELLM_ERR_UNSUPPORTED, "gemm_fused: covers M <= 64 tokens");
+    ONELLM_REQUIRE(K % 16 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED, "gemm_fused: need K %% 16 == 0, N %% 8 == 0");
+    ONELLM_REQUIRE(resid || !bias, ONELLM_ERR_ARG, "gemm_fused: bias is added with the residual; pass resid too");
+    ONELLM_REQUIRE(aligned16(x) && aligned16(W) && aligned16(y) && (!Wu || aligned16(Wu)), ONELLM_ERR_ARG,
+                   "gemm_fused: pointers must be 16-byte aligned");
+    ONELLM_REQUIRE(x != y, ONELLM_ERR_ARG, "gemm_fused: y must not alias x");
+    if (M == 0) return ONELLM_OK;
+    ONELLM_CUDA(skinny_kn_staged_dispatch((const __half*)x, (const __half*)W, (const __half*)Wu, (__half*)y, M, N, K, Wu != nullptr,
+                                          reinterpret_cast<cudaStream_t>(stream), (const __half*)resid, (const __half*)bias,
+                                          rms_eps));
+    return ONELLM_OK;
 }
 
 extern "C" int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, const void* Wu, void* out, int M,

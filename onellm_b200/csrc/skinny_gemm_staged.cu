@@ -71,11 +71,24 @@ struct FusedNormArgs {
     float eps;
 };
 
+// Options of the plain (not FUSED) kernel that let a decoder layer run without norm kernels:
+//   rms:   the result is scaled per token by rsqrt(mean_over_K(x^2) + rms_eps), i.e. the projection of
+//          RMSNorm(x) when the norm's gamma has been multiplied into the rows of W beforehand.  The sum
+//          of squares is taken from the activations as they pass through the ring (no extra reads).
+//   resid: y = resid + bias + result (bias may be NULL); resid may be y itself (each element is read
+//          and written by the same thread).
+struct EpilogueArgs {
+    const __half* resid;  // [M, N] or NULL
+    const __half* bias;   // [N] or NULL
+    float rms_eps;
+    int rms;
+};
+
 template <int MB, bool DUAL, bool FUSED>
 __global__ void __launch_bounds__(kStThreads)
 skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__ W0, const __half* __restrict__ W1,
-                        __half* __restrict__ y, int M, int N, int K, int stages_per_block, int nst,
-                        const FusedNormArgs fn)
+                        __half* y, int M, int N, int K, int stages_per_block, int nst,
+                        const FusedNormArgs fn, const EpilogueArgs ep)
 {
     constexpr int NW = DUAL ? 2 : 1;
     constexpr int MP = 8 * MB;
@@ -142,6 +155,9 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
         x_issued++;
     };
 
+    float ssq[MB];  // warp 0: this block's share of sum(x^2) per token (EpilogueArgs::rms)
+#pragma unroll
+    for (int mb = 0; mb < MB; mb++) ssq[mb] = 0.f;
     float acc[NW][MB][4];
 #pragma unroll
     for (int w = 0; w < NW; w++)
@@ -263,6 +279,15 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
                 xb[mb][0] = *reinterpret_cast<const uint32_t*>(p);
                 xb[mb][1] = *reinterpret_cast<const uint32_t*>(p + 16);
             }
+            if (!FUSED && ep.rms && warp == 0) {
+                // lane (g, t) holds x[token 8*mb + g][k = 2t, 2t+1, 2t+8, 2t+9] of this 16-row step
+#pragma unroll
+                for (int mb = 0; mb < MB; mb++) {
+                    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&xb[mb][0]));
+                    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&xb[mb][1]));
+                    ssq[mb] = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(b.x, b.x, fmaf(b.y, b.y, ssq[mb]))));
+                }
+            }
 #pragma unroll
             for (int w = 0; w < NW; w++) {
                 uint32_t a[4];
@@ -290,19 +315,39 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
                 const int c = warp * 16 + g + ((e & 2) ? 8 : 0);
                 red[(w * MP + tok) * kRedLd + c] = acc[w][mb][e];
             }
+    float* red_ss = red + NW * MP * kRedLd;  // [MP] partial sums of squares
+    if (!FUSED && ep.rms && warp == 0) {
+#pragma unroll
+        for (int mb = 0; mb < MB; mb++) {
+            float v = ssq[mb];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (t == 0) red_ss[8 * mb + g] = v;
+        }
+    }
     cluster.sync();
     const int per_rank = (MP * kBN + KS - 1) / KS;
     const int e_begin = rank * per_rank, e_end = min(e_begin + per_rank, MP * kBN);
     for (int e = e_begin + tid; e < e_end; e += kStThreads) {
         const int tok = e / kBN, c = e % kBN;
-        float s0 = 0.f, s1 = 0.f;
+        float s0 = 0.f, s1 = 0.f, ss = 0.f;
         for (int r = 0; r < KS; r++) {
             const float* peer = cluster.map_shared_rank(red, r);
             s0 += peer[tok * kRedLd + c];
             if (DUAL) s1 += peer[(MP + tok) * kRedLd + c];
+            if (!FUSED && ep.rms) ss += peer[NW * MP * kRedLd + tok];
         }
         if (tok < M && n0 + c < N) {
-            const float v = DUAL ? (s0 / (1.0f + __expf(-s0))) * s1 : s0;
+            if (!FUSED && ep.rms) {
+                const float inv = rsqrtf(ss / (float)K + ep.rms_eps);
+                s0 *= inv;
+                s1 *= inv;
+            }
+            float v = DUAL ? (s0 / (1.0f + __expf(-s0))) * s1 : s0;
+            if (!FUSED && ep.resid) {
+                v += __half2float(ep.resid[(size_t)tok * N + n0 + c]);
+                if (ep.bias) v += __half2float(ep.bias[n0 + c]);
+            }
             y[(size_t)tok * N + n0 + c] = __float2half_rn(v);
         }
     }
@@ -342,12 +387,12 @@ static int staged_slots(Kern kern, int ks, int nst, size_t smem, int col_blocks)
 
 template <int MB, bool DUAL, bool FUSED>
 static cudaError_t launch_staged(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K,
-                                 const FusedNormArgs& fn, cudaStream_t st)
+                                 const FusedNormArgs& fn, const EpilogueArgs& ep, cudaStream_t st)
 {
     auto kern = skinny_kn_staged_kernel<MB, DUAL, FUSED>;
     constexpr int NW = DUAL ? 2 : 1;
     constexpr size_t stage = (size_t)NW * kStageBytes + (FUSED ? 0 : 8 * MB * kXRowBytes);
-    constexpr size_t red = (size_t)NW * 8 * MB * kRedLd * sizeof(float);
+    constexpr size_t red = ((size_t)NW * 8 * MB * kRedLd + 8 * MB) * sizeof(float);
     constexpr size_t smem_cap = 226 * 1024;
     static bool attr_set = false;
     static std::mutex mu;
@@ -408,24 +453,26 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, per_block_final, best_nst, fn);
+    return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, per_block_final, best_nst, fn, ep);
 }
 
 // One pass of at most 64 tokens.  Called from skinny_gemm.cu.
 cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
-                                      int K, bool dual, cudaStream_t st)
+                                      int K, bool dual, cudaStream_t st, const __half* resid, const __half* bias,
+                                      float rms_eps)
 {
     const FusedNormArgs none = {nullptr, nullptr, nullptr, nullptr, 0.f};
+    const EpilogueArgs ep = {resid, resid ? bias : nullptr, rms_eps, rms_eps >= 0.f ? 1 : 0};
     if (dual) {
-        if (M <= 8) return launch_staged<1, true, false>(x, W0, W1, y, M, N, K, none, st);
-        if (M <= 16) return launch_staged<2, true, false>(x, W0, W1, y, M, N, K, none, st);
-        if (M <= 32) return launch_staged<4, true, false>(x, W0, W1, y, M, N, K, none, st);
-        return launch_staged<8, true, false>(x, W0, W1, y, M, N, K, none, st);
+        if (M <= 8) return launch_staged<1, true, false>(x, W0, W1, y, M, N, K, none, ep, st);
+        if (M <= 16) return launch_staged<2, true, false>(x, W0, W1, y, M, N, K, none, ep, st);
+        if (M <= 32) return launch_staged<4, true, false>(x, W0, W1, y, M, N, K, none, ep, st);
+        return launch_staged<8, true, false>(x, W0, W1, y, M, N, K, none, ep, st);
     }
-    if (M <= 8) return launch_staged<1, false, false>(x, W0, nullptr, y, M, N, K, none, st);
-    if (M <= 16) return launch_staged<2, false, false>(x, W0, nullptr, y, M, N, K, none, st);
-    if (M <= 32) return launch_staged<4, false, false>(x, W0, nullptr, y, M, N, K, none, st);
-    return launch_staged<8, false, false>(x, W0, nullptr, y, M, N, K, none, st);
+    if (M <= 8) return launch_staged<1, false, false>(x, W0, nullptr, y, M, N, K, none, ep, st);
+    if (M <= 16) return launch_staged<2, false, false>(x, W0, nullptr, y, M, N, K, none, ep, st);
+    if (M <= 32) return launch_staged<4, false, false>(x, W0, nullptr, y, M, N, K, none, ep, st);
+    return launch_staged<8, false, false>(x, W0, nullptr, y, M, N, K, none, ep, st);
 }
 
 }  // namespace onellm
@@ -455,13 +502,14 @@ extern "C" int onellm_add_residual_rmsnorm_gemm(int dtype, const void* x, const 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const __half *xh = (const __half*)x, *w0 = (const __half*)W, *w1 = (const __half*)Wu;
     __half* yh = (__half*)y;
+    const EpilogueArgs no_ep = {nullptr, nullptr, 0.f, 0};
     cudaError_t e;
     if (Wu)
-        e = M <= 8 ? launch_staged<1, true, true>(xh, w0, w1, yh, M, N, K, fn, st)
-                   : launch_staged<2, true, true>(xh, w0, w1, yh, M, N, K, fn, st);
+        e = M <= 8 ? launch_staged<1, true, true>(xh, w0, w1, yh, M, N, K, fn, no_ep, st)
+                   : launch_staged<2, true, true>(xh, w0, w1, yh, M, N, K, fn, no_ep, st);
     else
-        e = M <= 8 ? launch_staged<1, false, true>(xh, w0, nullptr, yh, M, N, K, fn, st)
-                   : launch_staged<2, false, true>(xh, w0, nullptr, yh, M, N, K, fn, st);
+        e = M <= 8 ? launch_staged<1, false, true>(xh, w0, nullptr, yh, M, N, K, fn, no_ep, st)
+                   : launch_staged<2, false, true>(xh, w0, nullptr, yh, M, N, K, fn, no_ep, st);
     ONELLM_REQUIRE(e == cudaSuccess, ONELLM_ERR_CUDA, "add_residual_rmsnorm_gemm: %s", cudaGetErrorString(e));
     return ONELLM_OK;
 }

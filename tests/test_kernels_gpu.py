@@ -269,7 +269,8 @@ def test_embedding(ob, cuda, orc, dt):
 
 
 @pytest.mark.parametrize("dt", ["f16", "f32"])
-@pytest.mark.parametrize("rows,V,K", [(8, 32000, 50), (64, 32000, 1), (3, 1000, 64), (2, 100, 7)])
+@pytest.mark.parametrize("rows,V,K", [(8, 32000, 50), (64, 32000, 1), (3, 1000, 64), (2, 100, 7), (2, 40000, 50), (3, 1003, 64),
+                                       (2, 32768, 64), (1, 32769, 5)])
 def test_topk_bit_exact(ob, cuda, orc, dt, rows, V, K):
     torch = cuda
     rng = np.random.default_rng(V + K)
@@ -281,6 +282,27 @@ def test_topk_bit_exact(ob, cuda, orc, dt, rows, V, K):
     rv, ri = orc.topk(x, K)
     assert np.array_equal(idx.cpu().numpy(), ri)
     assert np.array_equal(val.cpu().numpy(), rv)
+
+
+@pytest.mark.parametrize("dt", ["f16", "f32"])
+def test_topk_special_values(ob, cuda, orc, dt):
+    """All-equal rows (pure ties), NaN and infinities, negative-only rows."""
+    torch = cuda
+    V, K = 5000, 16
+    x = np.zeros((4, V), np.float32)
+    x[0, :] = 1.5                                   # every column ties: the K lowest columns win
+    x[1, :] = -np.arange(V, dtype=np.float32) - 1   # all negative
+    x[2, :] = 0.25
+    x[2, [7, 100, 4999]] = [np.inf, np.nan, -np.inf]
+    x[3, :] = _round(np.random.default_rng(3).standard_normal(V), dt)
+    x[3, ::2] = np.nan                               # half the row is NaN and must sort below everything
+    val = torch.zeros(4, K, device="cuda")
+    idx = torch.zeros(4, K, device="cuda", dtype=torch.int32)
+    ob.topk(ob.F16 if dt == "f16" else ob.F32, _dev(torch, _round(x, dt), dt), 4, V, K, val, idx)
+    rv, ri = orc.topk(_round(x, dt), K)
+    assert np.array_equal(idx.cpu().numpy(), ri)
+    assert np.array_equal(val.cpu().numpy(), rv)
+    assert ri[0].tolist() == list(range(K)) and ri[2, 0] == 7
 
 
 def test_topk_reference_case(ob, cuda):
@@ -355,6 +377,45 @@ def test_add_residual_rmsnorm_gemm_fused(ob, cuda, orc, M, N, K, dual, with_x, w
     with pytest.raises(ob.OnellmError):
         ob.add_residual_rmsnorm_gemm(ob.F16, d_r, d_r, None, _dev(torch, g, "f16"), 1e-5, d_r, _dev(torch, W, "f16"), None,
                                      y, M, N, K)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 40])
+@pytest.mark.parametrize("N,K,dual,rms,resid,with_bias", [
+    (12288, 4096, False, True, False, False),    # QKV behind the attention norm
+    (4096, 4096, False, False, True, True),      # o_proj adding into the residual stream
+    (11008, 4096, True, True, False, False),     # gate/up + SwiGLU behind the FFN norm
+    (4096, 11008, False, False, True, False),    # down_proj adding into the residual stream
+    (1376, 5120, True, True, True, True), (1000, 528, False, True, True, False),
+])
+def test_gemm_fused_norm_free_layer_ops(ob, cuda, orc, M, N, K, dual, rms, resid, with_bias):
+    """y = [resid + bias +] f(rsqrt(mean(x^2)+eps) * x . W): RMSNorm with gamma folded into W, and the residual add."""
+    torch = cuda
+    rng = np.random.default_rng(7 * M + N)
+    x = _round(3.0 * rng.standard_normal((M, K)), "f16")          # un-normalised residual-stream magnitudes
+    g = _round(1 + 0.1 * rng.standard_normal(K), "f16")
+    W = _round(0.02 * rng.standard_normal((K, N)), "f16")
+    Wu = _round(0.02 * rng.standard_normal((K, N)), "f16") if dual else None
+    r = _round(rng.standard_normal((M, N)), "f16") if resid else None
+    b = _round(0.1 * rng.standard_normal(N), "f16") if (resid and with_bias) else None
+    # the two sides of the identity the model relies on: norm kernel + projection == folded projection
+    Wf = _round(W * g[:, None], "f16") if rms else W
+    Wuf = (_round(Wu * g[:, None], "f16") if rms else Wu) if dual else None
+    if rms:
+        inv = 1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)
+        t0, t1 = orc.gemm(x, Wf) * inv, (orc.gemm(x, Wuf) * inv if dual else None)
+    else:
+        t0, t1 = orc.gemm(x, Wf), (orc.gemm(x, Wuf) if dual else None)
+    ref = orc.swiglu2(t0.astype(np.float32), t1.astype(np.float32)) if dual else t0
+    if resid:
+        ref = ref + r + (b if b is not None else 0.0)
+    y = _dev(torch, r, "f16") if resid else torch.zeros(M, N, device="cuda", dtype=torch.float16)
+    ob.gemm_fused(ob.F16, _dev(torch, x, "f16"), _dev(torch, Wf, "f16"), None if Wuf is None else _dev(torch, Wuf, "f16"), y, M, N, K,
+                  rms_eps=1e-5 if rms else -1.0, resid=y if resid else None, bias=None if b is None else _dev(torch, b, "f16"))
+    assert rel_err(y.float().cpu().numpy(), ref) < TOL["f16"]
+    if rms and not dual and not resid:
+        # and against the unfused reference order: RMSNorm (gamma applied, rounded to fp16), then x . W
+        xn = _round(orc.rmsnorm(x, g, 1e-5), "f16")
+        assert rel_err(y.float().cpu().numpy(), orc.gemm(xn, W)) < 2e-3
 
 
 @pytest.mark.parametrize("M,N,K,nk", [
