@@ -43,6 +43,11 @@ WORKLOADS = {
 METRIC = "decode tokens/s (Llama-7B shape, 1/2/4/8 B200); attn HBM GB/s vs peak"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel (gate/up + SwiGLU at this
+# exact shape), from the ncu capture summarised in profiles/skinny_kn_staged_gate_up_m8_4096x11008.md
+NCU_TRAFFIC_GATE_UP = 184_805_632
+NCU_TRAFFIC_SOURCE = "ncu capture of the same kernel and shape: 180.45 MB read + 4.36 MB written"
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -192,7 +197,7 @@ def kernel_rooflines(ob, torch, model, batch, ctx, hbm_peak):
     out = torch.empty(batch, I, device="cuda", dtype=torch.float16)
     t = timeit(lambda i: ob.gemm_swiglu(ob.F16, x, wg[i], wu[i], out, batch, I, h), n_rot)
     bytes_ = 2 * h * I * 2 + batch * h * 2 + batch * I * 2
-    res["gate_up_swiglu"] = {"kernel": "skinny_kn_staged_kernel<1,true>", "bytes": bytes_, "us": t * 1e6,
+    res["gate_up_swiglu"] = {"kernel": "skinny_kn_staged_kernel<1,true,false>", "bytes": bytes_, "us": t * 1e6,
                              "gbs": bytes_ / t / 1e9, "frac": bytes_ / t / 1e9 / hbm_peak}
     del wg, wu
     # down projection
@@ -201,7 +206,7 @@ def kernel_rooflines(ob, torch, model, batch, ctx, hbm_peak):
     y = torch.empty(batch, h, device="cuda", dtype=torch.float16)
     t = timeit(lambda i: ob.gemm(ob.F16, a, wd[i], y, batch, h, I), n_rot)
     bytes_ = h * I * 2 + batch * I * 2 + batch * h * 2
-    res["down_proj"] = {"kernel": "skinny_kn_staged_kernel<1,false>", "bytes": bytes_, "us": t * 1e6,
+    res["down_proj"] = {"kernel": "skinny_kn_staged_kernel<1,false,false>", "bytes": bytes_, "us": t * 1e6,
                         "gbs": bytes_ / t / 1e9, "frac": bytes_ / t / 1e9 / hbm_peak}
     del wd
     # decode attention at the given context: one layer's K and V are 2 x B*H*ctx*D*2 bytes
@@ -223,7 +228,7 @@ def kernel_rooflines(ob, torch, model, batch, ctx, hbm_peak):
 
     t = timeit(attn, n_rot)
     bytes_ = 2 * ctx * batch * H * D * 2 + 5 * batch * H * D * 2
-    res[f"decode_attn_ctx{ctx}"] = {"kernel": "decode_attn_kernel<__half,16,1> + combine", "bytes": bytes_,
+    res[f"decode_attn_ctx{ctx}"] = {"kernel": "decode_attn_mma_kernel<128,1>", "bytes": bytes_,
                                     "us": t * 1e6, "gbs": bytes_ / t / 1e9, "frac": bytes_ / t / 1e9 / hbm_peak}
     return res
 
@@ -332,7 +337,8 @@ def run_ours(args, workload):
         kr = kernel_rooflines(ob, torch, model, batch, 2048 - 8, hbm_peak)
         dom = kr["gate_up_swiglu"]
         line["roofline"] = {"bound": "hbm", "kernel": dom["kernel"], "achieved": dom["gbs"], "peak": hbm_peak,
-                            "unit": "GB/s", "frac": dom["frac"], "traffic": None, "peak_kind": peak_kind,
+                            "unit": "GB/s", "frac": dom["frac"], "traffic": NCU_TRAFFIC_GATE_UP, "traffic_source": NCU_TRAFFIC_SOURCE,
+                            "peak_kind": peak_kind,
                             "algorithmic_bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"]}
         line["kernels"] = kr
         if world == 1 and not args.no_cpu:
