@@ -251,7 +251,12 @@ def run_ours(args, workload):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         ids = [ob.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
-        m.init_comm(ids[0])
+        m.init_comm(ids[0])                       # NCCL: the context phase's large all-reduces
+        if not args.tp_nccl_only:
+            handles = [None] * world              # decode steps: one-shot all-reduce over peer memory
+            dist.all_gather_object(handles, m.p2p_handle())
+            m.p2p_connect(handles)
+            dist.barrier()
     m.init_random(seed=1234, std=0.02)
     m.set_sampling(top_k=top_k, temperature=temp)
     rng = np.random.default_rng(42)
@@ -321,6 +326,8 @@ def run_ours(args, workload):
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": workload, "batch": batch, "prompt_len": prompt_len, "max_seq_len": smax,
                            "top_k": top_k, "temperature": temp, "parallelism": f"tp{world}",
+                           "allreduce": ("none" if world == 1 else ("nccl" if args.tp_nccl_only else
+                                         "one-shot over peer memory, fused with the residual add (NCCL for the context phase)")),
                            "l2": "every step streams its weights and KV cache (>13 GB) once: inputs exceed the 126 MB L2",
                            "context_during_timing": [prompt_len + W, prompt_len + W + K],
                            "prefill": "skipped (cache seek, profiling)" if args.skip_prefill else "done before the timed region"},
@@ -358,6 +365,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b_decode_b8_p512", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--tp-nccl-only", action="store_true", help="N > 1: keep ncclAllReduce in the decode step (comparison)")
     ap.add_argument("--skip-prefill", action="store_true", help="profiling aid: seek to the prompt length instead of prefilling")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline leg")
     args = ap.parse_args()

@@ -327,6 +327,33 @@ ONELLM_API int onellm_topk_sample(const int* topk_id, const float* topk_val, int
                                   int* seqlen, unsigned char* finished, float* u_out, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * One-shot all-reduce over peer memory fused with the residual add, for tensor-parallel decode:
+ *
+ *     resid[i] <- resid[i] + bias[i % row_len] + sum over ranks of partial_r[i]          (F16)
+ *
+ * replacing ncclAllReduce + the add of launchFusedAddBiasResidualRMSNorm after o_proj and down_proj
+ * when the reference's decoder (src/layers/decoder/self_decoder.cpp:47-73) runs tensor parallel.
+ * One process per GPU on one node.  Every rank creates a communicator (which allocates its two send
+ * buffers and its flags), the 64-byte handles are exchanged by the host (any transport) and passed,
+ * in rank order, to onellm_p2p_connect.  Per call every rank first lets a kernel write its partial
+ * into onellm_p2p_send_buffer(which) on `stream`, then calls onellm_p2p_allreduce_add with the same
+ * `which`, n_elems and row_len on every rank; the two buffers must be used alternately (0, 1, 0, 1, ...),
+ * which keeps a rank from overwriting data a slower peer is still reading.  Sums are taken in rank
+ * order: every rank computes bit-identical results.  Waits for peers are bounded (about a second);
+ * onellm_p2p_error returns 1 once one has run out (the data of that call is then undefined).
+ * ------------------------------------------------------------------------------------- */
+#define ONELLM_P2P_HANDLE_BYTES 64
+typedef struct onellm_p2p onellm_p2p;
+ONELLM_API int onellm_p2p_create(int rank, int world, size_t max_elems, onellm_p2p** out);
+ONELLM_API int onellm_p2p_handle(onellm_p2p* comm, void* handle64);
+ONELLM_API int onellm_p2p_connect(onellm_p2p* comm, const void* handles /* world * 64 bytes, rank order */);
+ONELLM_API void* onellm_p2p_send_buffer(onellm_p2p* comm, int which);
+ONELLM_API int onellm_p2p_allreduce_add(onellm_p2p* comm, int dtype, int which, void* resid, const void* bias,
+                                        int n_elems, int row_len, void* stream);
+ONELLM_API int onellm_p2p_error(onellm_p2p* comm);
+ONELLM_API void onellm_p2p_destroy(onellm_p2p* comm);
+
+/* ---------------------------------------------------------------------------------------
  * LLaMA model: weights, KV cache and the generation loop (host side in C++).
  * Fills in the model class the reference leaves empty (src/models/llama/llama.h, outline in
  * src/models/llama/llama.cpp:1-50) with the kernel order of LlamaSelfDecoder::forward
@@ -366,6 +393,12 @@ ONELLM_API int onellm_llama_init_comm(onellm_llama* m, const void* id128);
 
 ONELLM_API int onellm_llama_set_sampling(onellm_llama* m, int top_k, float temperature, int literal_walk);
 ONELLM_API int onellm_llama_set_graphs(onellm_llama* m, int enabled);
+/* Tensor parallel over peer memory instead of NCCL for the decode step (batch * hidden small): every rank
+ * calls onellm_llama_p2p_handle, the host exchanges the handles, every rank calls onellm_llama_p2p_connect
+ * with all of them in rank order.  The context phase keeps using NCCL (onellm_llama_init_comm). */
+ONELLM_API int onellm_llama_p2p_handle(onellm_llama* m, void* handle64);
+ONELLM_API int onellm_llama_p2p_connect(onellm_llama* m, const void* handles);
+ONELLM_API int onellm_llama_p2p_error(onellm_llama* m);
 /* 1: run the context phase one position at a time through the decode kernels (cross-check path);
  * 0 (default): all prompt tokens at once through the context-phase kernels. */
 ONELLM_API int onellm_llama_set_prefill_by_decode(onellm_llama* m, int enabled);

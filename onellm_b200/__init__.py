@@ -222,6 +222,39 @@ def topk_sample(topk_id, topk_val, B, K, temperature, rng_step, vocab_size, end_
                                     _p(u_out), _stream(stream)))
 
 
+class P2p:
+    """The peer-memory all-reduce on its own (one object per process / GPU)."""
+
+    def __init__(self, rank, world, max_elems):
+        self._h = C.c_void_p()
+        _check(lib().onellm_p2p_create(C.c_int(rank), C.c_int(world), C.c_size_t(max_elems), C.byref(self._h)))
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        _check(lib().onellm_p2p_handle(self._h, buf))
+        return buf.raw
+
+    def connect(self, handles):
+        _check(lib().onellm_p2p_connect(self._h, C.c_char_p(b"".join(handles))))
+
+    def send_buffer(self, which) -> int:
+        f = lib().onellm_p2p_send_buffer
+        f.restype = C.c_void_p
+        return int(f(self._h, C.c_int(which)))
+
+    def allreduce_add(self, which, resid, bias, n_elems, row_len, stream=None):
+        _check(lib().onellm_p2p_allreduce_add(self._h, C.c_int(F16), C.c_int(which), _p(resid), _p(bias), C.c_int(n_elems),
+                                              C.c_int(row_len), _stream(stream)))
+
+    def error(self) -> int:
+        return int(lib().onellm_p2p_error(self._h))
+
+    def close(self):
+        if self._h:
+            lib().onellm_p2p_destroy(self._h)
+            self._h = C.c_void_p()
+
+
 def nccl_unique_id() -> bytes:
     buf = C.create_string_buffer(128)
     _check(lib().onellm_nccl_unique_id(buf))
@@ -267,6 +300,19 @@ class Llama:
 
     def init_comm(self, unique_id: bytes):
         _check(lib().onellm_llama_init_comm(self._h, C.c_char_p(unique_id)))
+
+    def p2p_handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        _check(lib().onellm_llama_p2p_handle(self._h, buf))
+        return buf.raw
+
+    def p2p_connect(self, handles):
+        """handles: the 64-byte handles of all ranks, in rank order."""
+        blob = b"".join(handles)
+        _check(lib().onellm_llama_p2p_connect(self._h, C.c_char_p(blob)))
+
+    def p2p_error(self) -> int:
+        return int(lib().onellm_llama_p2p_error(self._h))
 
     def set_sampling(self, top_k=1, temperature=1.0, literal_walk=False):
         _check(lib().onellm_llama_set_sampling(self._h, C.c_int(top_k), C.c_float(temperature),

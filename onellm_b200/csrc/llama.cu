@@ -160,6 +160,8 @@ struct Llama {
            *logits = nullptr;
     void* attn_ws = nullptr;
     size_t attn_ws_bytes = 0;
+    onellm_p2p* p2p = nullptr;  // peer-memory all-reduce of the decode step (tensor parallel)
+    bool p2p_connected = false;
     // state
     int batch = 0, cur_len = 0, prompt_cap = 0, graph_prompt_len = 0;
     int top_k = 1, literal_walk = 0;
@@ -319,9 +321,33 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
             m.launches += 1;
         }
         head_in = m.res;
+    } else if (m.p2p_connected) {
+        // tensor parallel over peer memory: o_proj and down_proj leave their partial sums in the two send
+        // buffers; one small kernel per projection reads every rank's partial over NVLink and adds the
+        // sum (and the bias) into this rank's copy of the residual stream.  No norm kernels, no NCCL.
+        __half* send0 = static_cast<__half*>(onellm_p2p_send_buffer(m.p2p, 0));
+        __half* send1 = static_cast<__half*>(onellm_p2p_send_buffer(m.p2p, 1));
+        RC(embedding_launch(ONELLM_F16, m.d_ids, m.res, nullptr, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
+        m.launches += 2;
+        for (int l = 0; l < c.num_layers; l++) {
+            const LayerW& L = m.layers[l];
+            RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w_qkv, nullptr, m.qkv, B, m.qkv_cols, h, c.rms_eps, nullptr, nullptr, sp));
+            RC(attention(l));
+            RC(onellm_gemm_fused(ONELLM_F16, m.attn, L.wo, nullptr, send0, B, h, m.Hl * D, -1.f, nullptr, nullptr, sp));
+            RC(onellm_p2p_allreduce_add(m.p2p, ONELLM_F16, 0, m.res, L.b_o, B * h, h, sp));
+            RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w1, L.w3, m.act, B, m.Il, h, c.rms_eps, nullptr, nullptr, sp));
+            RC(onellm_gemm_fused(ONELLM_F16, m.act, L.w2, nullptr, send1, B, h, m.Il, -1.f, nullptr, nullptr, sp));
+            RC(onellm_p2p_allreduce_add(m.p2p, ONELLM_F16, 1, m.res, nullptr, B * h, h, sp));
+            m.launches += 8;  // qkv, attention + combine, o, sum, gate/up, down, sum
+        }
+        if (mode & MODE_HEAD) {
+            RC(onellm_rmsnorm(ONELLM_F16, m.res, m.out_norm, c.rms_eps, B, h, sp));
+            m.launches += 1;
+        }
+        head_in = m.res;
     } else {
-        // tensor parallel: partial sums of o_proj and down_proj are all-reduced before the residual add,
-        // so the norm kernels stay (their per-layer gamma is all ones after finalize_weights)
+        // tensor parallel over NCCL: partial sums of o_proj and down_proj are all-reduced before the residual
+        // add, so the norm kernels stay (their per-layer gamma is all ones after finalize_weights)
         RC(embedding_launch(ONELLM_F16, m.d_ids, m.y, m.res, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
         RC(onellm_rmsnorm(ONELLM_F16, m.y, m.layers[0].attn_norm, c.rms_eps, B, h, sp));
         m.launches += 3;
@@ -616,6 +642,7 @@ extern "C" void onellm_llama_destroy(onellm_llama* h)
     cudaStreamSynchronize(m->stream);
     drop_graphs(*m);
     if (m->comm && nccl_api().CommDestroy) nccl_api().CommDestroy(m->comm);
+    if (m->p2p) onellm_p2p_destroy(m->p2p);
     if (m->stream) cudaStreamDestroy(m->stream);
     cudaFree(m->arena);
     if (m->pf_buf) cudaFree(m->pf_buf);
@@ -780,6 +807,36 @@ extern "C" int onellm_llama_set_sampling(onellm_llama* h, int top_k, float tempe
     m->temperature = temperature;
     m->literal_walk = literal_walk;
     return ONELLM_OK;
+}
+
+extern "C" int onellm_llama_p2p_handle(onellm_llama* h, void* handle64)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m && handle64, ONELLM_ERR_ARG, "llama_p2p_handle: null pointer");
+    ONELLM_REQUIRE(m->c.tp_size > 1, ONELLM_ERR_STATE, "llama_p2p_handle: tp_size is 1");
+    if (!m->p2p) {
+        const size_t elems = ((size_t)m->c.max_batch * m->c.hidden + 7) / 8 * 8;
+        RC(onellm_p2p_create(m->c.tp_rank, m->c.tp_size, elems, &m->p2p));
+    }
+    return onellm_p2p_handle(m->p2p, handle64);
+}
+
+extern "C" int onellm_llama_p2p_connect(onellm_llama* h, const void* handles)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m && handles, ONELLM_ERR_ARG, "llama_p2p_connect: null pointer");
+    ONELLM_REQUIRE(m->p2p, ONELLM_ERR_STATE, "llama_p2p_connect: call onellm_llama_p2p_handle first");
+    RC(onellm_p2p_connect(m->p2p, handles));
+    ONELLM_CUDA(cudaStreamSynchronize(m->stream));
+    drop_graphs(*m);
+    m->p2p_connected = true;
+    return ONELLM_OK;
+}
+
+extern "C" int onellm_llama_p2p_error(onellm_llama* h)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    return (m && m->p2p) ? onellm_p2p_error(m->p2p) : 0;
 }
 
 extern "C" int onellm_llama_set_graphs(onellm_llama* h, int enabled)

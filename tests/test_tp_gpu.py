@@ -11,7 +11,7 @@ CFG = dict(num_layers=2, hidden=512, head_num=8, kv_head_num=8, head_size=64, in
            max_seq_len=64, max_batch=4)
 
 
-def _worker(rank, size, port, prefix, q):
+def _worker(rank, size, port, prefix, q, p2p=False):
     import sys
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -24,14 +24,77 @@ def _worker(rank, size, port, prefix, q):
     dist.broadcast_object_list(ids, src=0)
     m = ob.Llama(**CFG, tp_rank=rank, tp_size=size)
     m.init_comm(ids[0])
+    if p2p:  # decode steps over peer memory; the context phase stays on NCCL
+        handles = [None] * size
+        dist.all_gather_object(handles, m.p2p_handle())
+        m.p2p_connect(handles)
+        dist.barrier()
     m.load_weights(prefix)
     prompt = np.random.default_rng(0).integers(0, CFG["vocab_size"], (3, 6)).astype(np.int32)
     out = m.generate(prompt, 5)
     logits = m.logits(3)
+    err = m.p2p_error() if p2p else 0
     if rank == 0:
-        q.put((out, logits))
+        q.put((out, logits, err))
     dist.barrier()
     m.close()
+    dist.destroy_process_group()
+
+
+def _p2p_worker(rank, size, port, q):
+    """The all-reduce on its own: 40 calls on alternating buffers, then one call the peer never joins."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch
+    import torch.distributed as dist
+    import onellm_b200 as ob
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=size)
+    rows, h = 8, 4096
+    n = rows * h
+    comm = ob.P2p(rank, size, n)
+    handles = [None] * size
+    dist.all_gather_object(handles, comm.handle())
+    comm.connect(handles)
+    dist.barrier()
+    gen = torch.Generator().manual_seed(11)
+    resid0 = torch.randn(rows, h, generator=gen).half()
+    bias = torch.randn(h, generator=gen).half()
+    parts = [[torch.randn(rows, h, generator=gen).half() for _ in range(size)] for _ in range(40)]  # same on every rank
+    resid = resid0.cuda()
+    d_bias = bias.cuda()
+    row_ids = torch.arange(rows, device="cuda", dtype=torch.int32)
+    want = resid0.clone()
+    ok = True
+    for i, per_rank in enumerate(parts):
+        which = i % 2
+        # the "projection": this rank's partial lands in the send buffer on the stream the all-reduce uses
+        dst = comm.send_buffer(which)
+        src = per_rank[rank].cuda()
+        ob.embedding(ob.F16, row_ids, dst, src, rows, h, rows)   # a row gather with ids 0..rows-1 = a device copy on this stream
+        comm.allreduce_add(which, resid, d_bias if which == 0 else None, n, h)
+        acc = want.float()
+        tot = torch.zeros_like(acc)
+        for r in range(size):
+            tot += per_rank[r].float()
+        acc = tot + acc + (bias.float() if which == 0 else 0.0)
+        want = acc.half()
+        if i % 10 == 9:
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(resid.cpu(), want)
+    torch.cuda.synchronize()
+    first_err = comm.error()
+    dist.barrier()
+    # a call the last rank never joins: the others give up after about a second and say so
+    timed_out = None
+    if rank != size - 1:
+        comm.allreduce_add(0, resid, None, n, h)
+        torch.cuda.synchronize()
+        timed_out = comm.error()
+    dist.barrier()
+    q.put((rank, ok, first_err, timed_out))
+    comm.close()
     dist.destroy_process_group()
 
 
@@ -58,10 +121,45 @@ def test_tp2_matches_tp1(ob, cuda, tmp_path):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, prefix, q)) for r in range(2)]
     for p in procs:
         p.start()
-    got, got_logits = q.get(timeout=300)
+    got, got_logits, _ = q.get(timeout=300)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
     assert np.abs(got_logits - want_logits).max() / np.abs(want_logits).max() < 3e-3
     # greedy ids agree unless two logits tie within fp16 rounding; report rather than require all
     assert (got == want).mean() > 0.8
+    # the same with the decode steps' all-reduce over peer memory
+    q2 = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port + 1 if port < 65000 else port - 1, prefix, q2, True)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got2, got_logits2, err = q2.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert err == 0
+    assert np.abs(got_logits2 - want_logits).max() / np.abs(want_logits).max() < 3e-3
+    assert (got2 == want).mean() > 0.8
+
+
+def test_p2p_allreduce_add_bit_exact_and_bounded_wait(ob, cuda):
+    torch = cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    size = 2
+    procs = [ctx.Process(target=_p2p_worker, args=(r, size, port, q)) for r in range(size)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in range(size))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, ok, first_err, timed_out in results:
+        assert ok and first_err == 0, (rank, ok, first_err)          # every rank holds the same, exact, sums
+        assert timed_out == (1 if rank != size - 1 else None)        # the wait ran out, the kernel returned
