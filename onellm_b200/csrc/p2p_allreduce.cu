@@ -50,13 +50,14 @@ struct P2pPeers {
     P2pControl* ctl[kP2pMaxWorld];     // control block of every rank (own included)
 };
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) { asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ int ld_acquire_sys(const int* p)
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) { asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ int ld_relaxed_sys(const int* p)
 {
     int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void fence_acquire_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
 __device__ __forceinline__ unsigned long long global_ns()
 {
@@ -92,16 +93,18 @@ p2p_allreduce_add_kernel(const P2pPeers peers, int rank, int world, __half* __re
     const int seq = s_seq;
     if (threadIdx.x < world) {
         const int p = threadIdx.x;
-        __threadfence_system();
-        st_release_sys(&peers.ctl[p]->flags[b][rank], seq);  // "partial number seq of rank `rank` is complete"
+        // "partial number seq of rank `rank` is complete".  No release fence is needed in front of the store:
+        // the partial was written by the kernel before this one, whose completion (griddepcontrol.wait above)
+        // has already made it visible at system scope.
+        st_relaxed_sys(&peers.ctl[p]->flags[b][rank], seq);
         const unsigned long long t0 = global_ns();
-        while (ld_acquire_sys(&mine->flags[b][p]) < seq) {
+        while (ld_relaxed_sys(&mine->flags[b][p]) < seq) {
             if (global_ns() - t0 > kP2pWaitNs) {
                 atomicExch(&mine->error, 1);
                 break;
             }
-            __nanosleep(20);
         }
+        fence_acquire_sys();  // the peer's partial is read only after its flag has been seen
     }
     __syncthreads();
     const int n_vec = n_elems / 8;

@@ -172,9 +172,10 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
     // dependent launch; a no-op for a plain launch).  The next kernel in the stream is released
     // either here (EpilogueArgs::early_dependents: hides its launch latency; measured 2 % faster over
     // a decode step) or after the main loop.
+    // one commit group per stage: the first stage can be consumed as soon as ITS weights have landed
     for (int s = 0; s < nst - 1; s++) {
         issue_w(smem_base + (uint32_t)(s * STAGE));
-        if (FUSED) cp_async_commit();
+        cp_async_commit();
     }
     if (ep.early_dependents) pdl_launch_dependents();
     pdl_wait();
@@ -244,10 +245,26 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
         }
         // visibility to the other warps: the barrier at the top of the main loop
     } else {
-        for (int s = 0; s < nst - 1; s++) {
-            issue_x(smem_base + (uint32_t)(s * STAGE));
-            cp_async_commit();  // group 0 also carries every weight copy issued above
+        // Activations of the stages already on their way: plain loads (they sit in L2, the producer has
+        // just written them) stored to shared memory by the thread that will later copy them
+        // asynchronously.  Had they joined the ring as one more copy group, the first stage would have
+        // to wait for every weight copy issued above.
+        constexpr int kMaxPro = 11;  // ring depth is at most 12
+        if (x_thread) {
+            uint4 xv[kMaxPro];
+#pragma unroll
+            for (int s = 0; s < kMaxPro; s++) {
+                xv[s] = make_uint4(0u, 0u, 0u, 0u);
+                if (s < nst - 1 && s < n_stages && k_begin + s * kKC + x_part * 8 < k_end)
+                    xv[s] = *reinterpret_cast<const uint4*>(xsrc + (size_t)s * kKC);
+            }
+#pragma unroll
+            for (int s = 0; s < kMaxPro; s++)
+                if (s < nst - 1) *reinterpret_cast<uint4*>(smem + (size_t)s * STAGE + xdst) = xv[s];
+            xsrc += (size_t)(nst - 1) * kKC;
         }
+        x_issued = nst - 1;
+        // visible to the other warps through the barrier at the top of the main loop
     }
     uint32_t cons = 0, fill = (uint32_t)((nst - 1) * STAGE);  // byte offsets of the slot consumed / refilled
     const uint32_t ring_bytes = (uint32_t)(nst * STAGE);
@@ -332,12 +349,25 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
     const int e_begin = rank * per_rank, e_end = min(e_begin + per_rank, MP * kBN);
     for (int e = e_begin + tid; e < e_end; e += kStThreads) {
         const int tok = e / kBN, c = e % kBN;
+        // all remote loads are issued before the first is used (a cluster has at most 8 ranks): summing as
+        // they are requested would pay one distributed-shared-memory round trip per rank
+        float p0[8], p1[8], ps[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            p0[r] = p1[r] = ps[r] = 0.f;
+            if (r < KS) {
+                const float* peer = cluster.map_shared_rank(red, r);
+                p0[r] = peer[tok * kRedLd + c];
+                if (DUAL) p1[r] = peer[(MP + tok) * kRedLd + c];
+                if (!FUSED && ep.rms) ps[r] = peer[NW * MP * kRedLd + tok];
+            }
+        }
         float s0 = 0.f, s1 = 0.f, ss = 0.f;
-        for (int r = 0; r < KS; r++) {
-            const float* peer = cluster.map_shared_rank(red, r);
-            s0 += peer[tok * kRedLd + c];
-            if (DUAL) s1 += peer[(MP + tok) * kRedLd + c];
-            if (!FUSED && ep.rms) ss += peer[NW * MP * kRedLd + tok];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {  // rank order: the sum does not depend on which block does it
+            s0 += p0[r];
+            s1 += p1[r];
+            ss += ps[r];
         }
         if (tok < M && n0 + c < N) {
             if (!FUSED && ep.rms) {

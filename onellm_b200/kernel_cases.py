@@ -23,21 +23,27 @@ def main():
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2040)
+    ap.add_argument("--graph", action="store_true", help="time a CUDA graph of the launches (device-side back-to-back)")
+    ap.add_argument("--tp", type=int, default=1, help="per-rank shapes of a tensor-parallel degree (heads and FFN columns divided)")
     a = ap.parse_args()
     B = a.batch
+    global H_, INTER
+    H_, INTER = H_ // a.tp, INTER // a.tp
+    QKV_N, ATT_K = 3 * HID // a.tp, HID // a.tp
     torch.cuda.set_device(0)
     torch.manual_seed(0)
     st = torch.cuda.current_stream()
     rnd = lambda *s: (0.02 * torch.randn(*s, device="cuda")).half()
     rot = 3
     if a.case == "gate_up":
+        rot = max(3, int(400e6 // (HID * INTER * 4)) + 1)
         x, wg, wu = torch.randn(B, HID, device="cuda").half(), [rnd(HID, INTER) for _ in range(rot)], [rnd(HID, INTER) for _ in range(rot)]
         out = torch.empty(B, INTER, device="cuda", dtype=torch.float16)
         fn = lambda i: ob.gemm_swiglu(ob.F16, x, wg[i], wu[i], out, B, INTER, HID)
         nbytes = 2 * HID * INTER * 2 + B * HID * 2 + B * INTER * 2
     elif a.case in ("down", "qkv", "o_proj"):
-        K, N = {"down": (INTER, HID), "qkv": (HID, 3 * HID), "o_proj": (HID, HID)}[a.case]
-        rot = 5 if a.case == "o_proj" else 3
+        K, N = {"down": (INTER, HID), "qkv": (HID, QKV_N), "o_proj": (ATT_K, HID)}[a.case]
+        rot = max(3, int(400e6 // (K * N * 2)) + 1)
         x, w = torch.randn(B, K, device="cuda").half(), [rnd(K, N) for _ in range(rot)]
         out = torch.empty(B, N, device="cuda", dtype=torch.float16)
         fn = lambda i: ob.gemm(ob.F16, x, w[i], out, B, N, K, ob.W_KN)
@@ -100,11 +106,24 @@ def main():
         fn(i % rot)
     st.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(st)
-    for i in range(a.iters):
-        fn(i % rot)
-    e1.record(st)
-    st.synchronize()
+    if a.graph:
+        # the launches of one timing pass as a CUDA graph: back to back on the device, no host launch cost
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(a.iters):
+                fn(i % rot)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    else:
+        e0.record(st)
+        for i in range(a.iters):
+            fn(i % rot)
+        e1.record(st)
+        st.synchronize()
     t = e0.elapsed_time(e1) / a.iters * 1e-3
     if a.case.startswith("prefill_"):
         print(f"{a.case}: {t * 1e6:.1f} us/launch, {nbytes / t / 1e12:.0f} TFLOP/s ({nbytes} flops), timeout flag "
