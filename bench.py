@@ -38,6 +38,8 @@ WORKLOADS = {
     # name: (model, batch, prompt_len, max_seq_len, top_k, temperature)
     "llama7b_decode_b8_p512": (MODEL_7B, 8, 512, 2048, 50, 1.0),
     "llama7b_decode_b8_ctx2040": (MODEL_7B, 8, 1912, 2048, 50, 1.0),
+    # BASELINE.json configs[4] (the tensor-parallel configuration; 133 GB of weights + cache also fit one GPU)
+    "llama13b_decode_b64_ctx2000": (MODEL_13B, 64, 2000, 2048, 50, 0.8),
     "llama13b_decode_b64_ctx2040": (MODEL_13B, 64, 1912, 2048, 50, 0.8),
 }
 METRIC = "decode tokens/s (Llama-7B shape, 1/2/4/8 B200); attn HBM GB/s vs peak"

@@ -32,7 +32,7 @@ constexpr int kP2pMaxWorld = 8;
 constexpr int kP2pMaxBlocks = 64;
 constexpr int kP2pThreads = 256;
 constexpr int kP2pVecPerThread = 4;                       // 16-byte vectors per thread
-constexpr unsigned long long kP2pWaitNs = 1000ULL * 1000 * 1000;  // a wait for a peer gives up after one second
+constexpr long long kP2pWaitCycles = 2000LL * 1000 * 1000;  // a wait for a peer gives up after about a second of SM clocks
 
 // Layout of the block every rank allocates and exports:
 //   [0]            control: flags[kP2pMaxBlocks][kP2pMaxWorld] (written by peers), counters[kP2pMaxBlocks], error
@@ -58,13 +58,6 @@ __device__ __forceinline__ int ld_relaxed_sys(const int* p)
     return v;
 }
 __device__ __forceinline__ void fence_acquire_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
-
-__device__ __forceinline__ unsigned long long global_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 
 // peer data is read once per call, after the acquire on the peer's flag: a system-scope load that
 // bypasses the non-coherent path
@@ -97,9 +90,9 @@ p2p_allreduce_add_kernel(const P2pPeers peers, int rank, int world, __half* __re
         // the partial was written by the kernel before this one, whose completion (griddepcontrol.wait above)
         // has already made it visible at system scope.
         st_relaxed_sys(&peers.ctl[p]->flags[b][rank], seq);
-        const unsigned long long t0 = global_ns();
+        const long long t0 = clock64();  // the SM's own cycle counter: reading it costs nothing next to the poll
         while (ld_relaxed_sys(&mine->flags[b][p]) < seq) {
-            if (global_ns() - t0 > kP2pWaitNs) {
+            if (clock64() - t0 > kP2pWaitCycles) {
                 atomicExch(&mine->error, 1);
                 break;
             }
