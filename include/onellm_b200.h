@@ -407,6 +407,11 @@ ONELLM_API int onellm_llama_set_prefill_by_decode(onellm_llama* m, int enabled);
  * sequence state.  host_first_ids (may be NULL) receives the first generated token per prompt. */
 ONELLM_API int onellm_llama_prefill(onellm_llama* m, const int* host_ids, int batch, int prompt_len,
                                     int* host_first_ids);
+/* A further turn of the same `batch` sequences: n_new more tokens each (host ids [batch, n_new]) behind
+ * the positions already in the KV cache, through the context-phase kernels with history_length =
+ * the current length (the multi-turn case of src/layers/decoder/context_decoder.cpp:36-134).
+ * host_first_ids (may be NULL) receives the next generated token per sequence. */
+ONELLM_API int onellm_llama_extend(onellm_llama* m, const int* host_ids, int n_new, int* host_first_ids);
 /* Declares cur_len positions of `batch` sequences as already present in the KV cache and host_ids
  * [batch] as the next input tokens (resume on a cache filled elsewhere; profiling without prefill). */
 ONELLM_API int onellm_llama_seek(onellm_llama* m, int batch, int cur_len, const int* host_ids);

@@ -333,6 +333,15 @@ class Llama:
                                           C.c_int(ids.shape[1]), out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def extend(self, ids):
+        """ids [batch, n_new]: a further turn behind the cached positions; returns the next token per sequence."""
+        import numpy as np
+        ids = np.ascontiguousarray(ids, np.int32)
+        first = np.zeros(ids.shape[0], np.int32)
+        _check(lib().onellm_llama_extend(self._h, ids.ctypes.data_as(C.c_void_p), C.c_int(ids.shape[1]),
+                                         first.ctypes.data_as(C.c_void_p)))
+        return first
+
     def seek(self, batch, cur_len, ids):
         import numpy as np
         ids = np.ascontiguousarray(ids, np.int32)

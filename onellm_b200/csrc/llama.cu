@@ -439,7 +439,7 @@ static int run_step(Llama& m, int mode, int prompt_len)
 // fused QKV bias + RoPE + cache write, causal attention over the cache, then the LM head on the
 // last token of every sequence.  Same arithmetic as running the positions one by one through the
 // decode kernels (which `prefill_by_decode` still does, for cross-checking).
-static int prefill_context(Llama& m, int B, int P)
+static int prefill_context(Llama& m, int B, int P, int history)
 {
     const auto& c = m.c;
     const int h = c.hidden, D = c.head_size;
@@ -467,7 +467,7 @@ static int prefill_context(Llama& m, int B, int P)
     __half* act2 = cv.take<__half>(T * (size_t)m.Il);
     int* d_cu = cv.take<int>(c.max_batch + 1);
     int* d_hist = cv.take<int>(c.max_batch);
-    std::vector<int> cu(B + 1), hist(B, 0);
+    std::vector<int> cu(B + 1), hist(B, history);
     for (int b = 0; b <= B; b++) cu[b] = b * P;
     ONELLM_CUDA(cudaMemcpyAsync(d_cu, cu.data(), (B + 1) * sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemcpyAsync(d_hist, hist.data(), B * sizeof(int), cudaMemcpyHostToDevice, st));
@@ -512,7 +512,7 @@ static int prefill_context(Llama& m, int B, int P)
     RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
                           m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
     m.launches += 5;
-    m.cur_len = P;
+    m.cur_len = history + P;
     return ONELLM_OK;
 }
 
@@ -875,7 +875,7 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
         for (int p = 0; p < prompt_len; p++)
             RC(run_step(*m, MODE_GATHER | (p == prompt_len - 1 ? MODE_HEAD : 0), prompt_len));
     } else {
-        RC(prefill_context(*m, batch, prompt_len));
+        RC(prefill_context(*m, batch, prompt_len, 0));
     }
     if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
     ONELLM_CUDA(cudaStreamSynchronize(st));
@@ -884,6 +884,31 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
     ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_prefill: token id outside [0, vocab_size)");
     ONELLM_REQUIRE(bad[1] == 0, ONELLM_ERR_STATE, "llama_prefill: a position beyond max_seq_len was refused by the cache");
     ONELLM_REQUIRE(onellm_gemm_timeout_flag() <= 0, ONELLM_ERR_CUDA, "llama_prefill: a tensor-core GEMM block timed out");
+    return ONELLM_OK;
+}
+
+// A further turn: n_new more tokens per sequence behind the cur_len positions already cached (history),
+// through the context-phase kernels; the sampler is seeded with the new length, as after a prefill.
+extern "C" int onellm_llama_extend(onellm_llama* h, const int* host_ids, int n_new, int* host_first_ids)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m && host_ids, ONELLM_ERR_ARG, "llama_extend: null pointer");
+    ONELLM_REQUIRE(m->batch > 0 && m->cur_len > 0, ONELLM_ERR_STATE, "llama_extend: call prefill first");
+    ONELLM_REQUIRE(n_new >= 1 && m->cur_len + n_new <= m->c.max_seq_len, ONELLM_ERR_ARG,
+                   "llama_extend: %d cached + %d new positions exceed max_seq_len %d", m->cur_len, n_new, m->c.max_seq_len);
+    cudaStream_t st = m->stream;
+    const int batch = m->batch, new_len = m->cur_len + n_new;
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_prompt, host_ids, (size_t)batch * n_new * sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &new_len, sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaStreamSynchronize(st));  // `new_len` lives on this stack frame
+    RC(prefill_context(*m, batch, n_new, m->cur_len));
+    if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
+    ONELLM_CUDA(cudaStreamSynchronize(st));
+    int bad[2] = {0, 0};
+    ONELLM_CUDA(cudaMemcpy(bad, m->d_bad_id, 2 * sizeof(int), cudaMemcpyDeviceToHost));
+    ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_extend: token id outside [0, vocab_size)");
+    ONELLM_REQUIRE(bad[1] == 0, ONELLM_ERR_STATE, "llama_extend: a position beyond max_seq_len was refused by the cache");
+    ONELLM_REQUIRE(onellm_gemm_timeout_flag() <= 0, ONELLM_ERR_CUDA, "llama_extend: a tensor-core GEMM block timed out");
     return ONELLM_OK;
 }
 

@@ -102,6 +102,31 @@ def test_random_init_statistics(ob, cuda):
     m.close()
 
 
+def test_second_turn_with_history_matches_one_long_prompt(ob, cuda, orc, tmp_path):
+    """prefill(40) + extend(30) (context kernels with history 40) == prefill(70); decoding continues from there."""
+    cfg = dict(CFG, max_seq_len=128)
+    m, w = _make(ob, tmp_path, cfg, seed=11)
+    ids = np.random.default_rng(6).integers(0, cfg["vocab_size"], (3, 70)).astype(np.int32)
+    want_first = m.prefill(ids)
+    want = m.logits(3)
+    want_next = np.zeros(3, np.int32)
+    m.decode_step(None, want_next)
+    want2 = m.logits(3)
+    m.prefill(ids[:, :40])
+    got_first = m.extend(ids[:, 40:])
+    got = m.logits(3)
+    assert rel_err(got, want) < 2e-3
+    assert np.array_equal(got_first, orc.topk(got, 1)[1][:, 0])
+    got_next = np.zeros(3, np.int32)
+    m.decode_step(None, got_next)
+    assert m.state()[0] == 71
+    if np.array_equal(got_first, want_first):     # same token fed in both runs (a near-tie could differ)
+        assert rel_err(m.logits(3), want2) < 3e-3
+    with pytest.raises(ob.OnellmError):
+        m.extend(np.zeros((3, 100), np.int32))          # 71 + 100 > max_seq_len
+    m.close()
+
+
 def test_context_phase_matches_position_by_position(ob, cuda, tmp_path):
     """A 100-token prompt (tensor-core GEMMs, M = 300) against the same prompt fed one position at a time."""
     cfg = dict(CFG, max_seq_len=128)
