@@ -4,13 +4,15 @@
 // src/kernels/cublas_wrapper.cc:45-90 of the reference) for prefill shapes: y[M,N] = x[M,K] . W with
 // W [K,N] (the layer weights, N contiguous) or W [N,K] (the LM head), fp16 in, fp32 accumulate.
 //
-// One 128 x 128 output tile per block.  A producer thread streams 64-deep K slices of both
-// operands into a ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle;
-// no cluster multicast anywhere); an MMA thread issues tcgen05.mma (M = 128, N = 128, K = 16,
-// kind::f16) with the accumulator in tensor memory and releases each stage with tcgen05.commit;
-// after the last slice all four warps read the accumulator with tcgen05.ld, convert and store.
+// One 128 x 256 output tile per block (with 128 x 128 tiles the operand traffic from L2 into shared
+// memory, 15.6 KB per MFLOP, was what bounded the kernel; the wider tile needs 11.7).  A producer
+// thread streams 64-deep K slices of both operands into a ring of four shared-memory stages with TMA
+// (cp.async.bulk.tensor, 128-byte swizzle; no cluster multicast anywhere); an MMA thread issues
+// tcgen05.mma (M = 128, N = 256, K = 16, kind::f16) with the accumulator in tensor memory (256 columns)
+// and releases each stage with tcgen05.commit; after the last slice all four warps read the
+// accumulator with tcgen05.ld, convert and store.
 // The [K,N] weight is used as it lies in memory: it is the "MN-major" B operand of the MMA
-// (two 64-column TMA boxes per stage), so no transposed copy of the weights is ever made.
+// (four 64-column TMA boxes per stage), so no transposed copy of the weights is ever made.
 // Every wait on an mbarrier is bounded; on a time-out the block records it in a device flag,
 // skips its stores, frees its tensor memory and exits.
 #include <cuda.h>
@@ -21,12 +23,13 @@
 
 namespace onellm {
 
-constexpr int kTcBM = 128, kTcBN = 128, kTcBK = 64;
-constexpr int kTcStages = 3;
+constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64;
+constexpr int kTcStages = 4;
 constexpr int kTcBand = 16;  // row tiles per band of the tile order
 constexpr int kTcThreads = 128;
 constexpr int kTcATile = kTcBM * kTcBK * 2;        // 16 KB: 128 rows x 128 bytes
-constexpr int kTcBTile = kTcBN * kTcBK * 2;        // 16 KB: [K,N] two boxes of 64 k-rows x 128 bytes; [N,K] 128 rows x 128 bytes
+constexpr int kTcBTile = kTcBN * kTcBK * 2;        // 32 KB: [K,N] four boxes of 64 k-rows x 128 bytes; [N,K] 256 rows x 128 bytes
+constexpr int kTcBChunk = 64 * kTcBK * 2;          // 8 KB: one 64-column chunk of a [K,N] stage
 constexpr int kTcStageBytes = kTcATile + kTcBTile;
 constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr uint32_t kSpinLimit = 1u << 24;  // ~0.3 s of polling
@@ -97,7 +100,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 }
 
 // W_NK = false: W [K,N] (B operand MN-major);  W_NK = true: W [N,K] (B operand K-major).
-// grid = (ceil(N/128), ceil(M/128)).
+// grid = one block per 128 x 256 tile, in band order (see the kernel).
 template <bool W_NK>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -135,7 +138,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 2) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTcBN)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -159,12 +162,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (W_NK) {
                 tma_load_2d(b_dst, &map_b, ks * kTcBK, n0, full0 + 8 * s);
             } else {
-                tma_load_2d(b_dst, &map_b, n0, ks * kTcBK, full0 + 8 * s);
-                tma_load_2d(b_dst + kTcBTile / 2, &map_b, n0 + 64, ks * kTcBK, full0 + 8 * s);
+#pragma unroll
+                for (int c = 0; c < kTcBN / 64; c++)
+                    tma_load_2d(b_dst + c * kTcBChunk, &map_b, n0 + 64 * c, ks * kTcBK, full0 + 8 * s);
             }
         }
     } else if (warp == 1 && lane == 0) {
-        // instruction descriptor: D = f32, A = B = f16, A K-major, B MN-major unless W_NK, N = 128, M = 128
+        // instruction descriptor: D = f32, A = B = f16, A K-major, B MN-major unless W_NK, N = 256, M = 128
         const uint32_t idesc = (1u << 4) | ((W_NK ? 0u : 1u) << 16) | ((uint32_t)(kTcBN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
         for (int ks = 0; ks < k_steps && ok; ks++) {
             const int s = ks % kTcStages;
@@ -178,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint64_t adesc = umma_desc(a_addr + kk * 32, 16, 1024);
                 // B [N,K]: same form.  B [K,N]: MN-major, 64-column chunks 8192 bytes apart (LBO), 8-row k groups
                 // 1024 bytes apart (SBO); 16 k = two groups further
-                const uint64_t bdesc = W_NK ? umma_desc(b_addr + kk * 32, 16, 1024) : umma_desc(b_addr + kk * 2048, kTcBTile / 2, 1024);
+                const uint64_t bdesc = W_NK ? umma_desc(b_addr + kk * 32, 16, 1024) : umma_desc(b_addr + kk * 2048, kTcBChunk, 1024);
                 umma_f16(tmem_base, adesc, bdesc, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
@@ -218,7 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 2) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTcBN) : "memory");
     }
 }
 
