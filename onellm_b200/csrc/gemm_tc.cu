@@ -17,6 +17,7 @@
 // skips its stores, frees its tensor memory and exits.
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -26,12 +27,13 @@ namespace onellm {
 constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64;
 constexpr int kTcStages = 4;
 constexpr int kTcBand = 16;  // row tiles per band of the tile order
-constexpr int kTcThreads = 128;
+constexpr int kTcThreads = 192;      // producer warp, MMA warp, four epilogue warps
+constexpr int kTcEpiThreads = 128;
 constexpr int kTcATile = kTcBM * kTcBK * 2;        // 16 KB: 128 rows x 128 bytes
 constexpr int kTcBTile = kTcBN * kTcBK * 2;        // 32 KB: [K,N] four boxes of 64 k-rows x 128 bytes; [N,K] 256 rows x 128 bytes
 constexpr int kTcBChunk = 64 * kTcBK * 2;          // 8 KB: one 64-column chunk of a [K,N] stage
 constexpr int kTcStageBytes = kTcATile + kTcBTile;
-constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + 1024 /* alignment slack */ + 256 /* barriers, TMEM address */;
 constexpr uint32_t kSpinLimit = 1u << 24;  // ~0.3 s of polling
 
 __device__ int g_tc_timeout_flag;  // set when a bounded wait gave up
@@ -99,8 +101,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // W_NK = false: W [K,N] (B operand MN-major);  W_NK = true: W [N,K] (B operand K-major).
-// grid = one block per 128 x 256 tile, in band order (see the kernel).
+// Persistent: grid = min(tiles, SMs) blocks of six warps; block c works on tiles c, c + grid, ... in band
+// order (see below).  Warp 0 (one thread) is the TMA producer, warp 1 (one thread) issues the MMAs,
+// warps 2-5 are the epilogue.  Tensor memory holds TWO 128 x 256 accumulators, so the MMAs of the next
+// tile run while the epilogue warps drain the previous one.
 template <bool W_NK>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -110,23 +120,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // 1024-byte alignment for the 128-byte swizzle pattern
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTcStages * kTcStageBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 1);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcStages), accum_bar = smem_u32(bars + 2 * kTcStages);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kTcStages + 4);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kTcStages);
+    const uint32_t acc_full0 = smem_u32(bars + 2 * kTcStages), acc_empty0 = smem_u32(bars + 2 * kTcStages + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Tile order: the linear block index walks down a band of kTcBand row tiles, then moves one column
-    // tile to the right, so the blocks resident at one time (about two per SM) cover a near-square patch
+    // Tile order: the linear tile index walks down a band of kTcBand row tiles, then moves one column
+    // tile to the right, so the tiles in flight at one time (one per SM) cover a near-square patch
     // of the output and share their A row blocks and B column blocks in L2.  (Row-major order made every
     // wave touch all column tiles of B: operands were read from DRAM seven times over.)
     const int tiles_m = (M + kTcBM - 1) / kTcBM, tiles_n = (N + kTcBN - 1) / kTcBN;
-    int tile_m, tile_n;
-    {
+    const int n_tiles = tiles_m * tiles_n;
+    auto tile_origin = [&](int t, int& m0, int& n0) {
         const int per_band = kTcBand * tiles_n;
-        const int band = blockIdx.x / per_band, in_band = blockIdx.x % per_band;
+        const int band = t / per_band, in_band = t % per_band;
         const int band_rows = min(kTcBand, tiles_m - band * kTcBand);
-        tile_m = band * kTcBand + in_band % band_rows;
-        tile_n = in_band / band_rows;
-    }
-    const int n0 = tile_n * kTcBN, m0 = tile_m * kTcBM;
+        m0 = (band * kTcBand + in_band % band_rows) * kTcBM;
+        n0 = (in_band / band_rows) * kTcBN;
+    };
     const int k_steps = (K + kTcBK - 1) / kTcBK;
 
     if (threadIdx.x == 0) {
@@ -134,11 +144,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int a = 0; a < 2; a++) {
+            mbar_init(acc_full0 + 8 * a, 1);
+            mbar_init(acc_empty0 + 8 * a, kTcEpiThreads);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 2) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTcBN)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2u * kTcBN)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -149,80 +162,105 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     pdl_wait();  // x comes from the previous kernel in the stream
 
-    bool ok = true;
     if (warp == 0 && lane == 0) {
-        // producer: one 64-deep slice of A and of B per stage
-        for (int ks = 0; ks < k_steps && ok; ks++) {
-            const int s = ks % kTcStages;
-            if (ks >= kTcStages) ok = mbar_wait(empty0 + 8 * s, ((ks / kTcStages) - 1) & 1);
-            if (!ok) break;
-            const uint32_t a_dst = smem_u32(smem + s * kTcStageBytes), b_dst = a_dst + kTcATile;
-            mbar_expect_tx(full0 + 8 * s, kTcStageBytes);
-            tma_load_2d(a_dst, &map_a, ks * kTcBK, m0, full0 + 8 * s);
-            if (W_NK) {
-                tma_load_2d(b_dst, &map_b, ks * kTcBK, n0, full0 + 8 * s);
-            } else {
+        // producer: one 64-deep slice of A and of B per stage, tile after tile
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+            int m0, n0;
+            tile_origin(t, m0, n0);
+            for (int ks = 0; ks < k_steps; ks++, it++) {
+                const int s = it % kTcStages;
+                if (it >= kTcStages) ok = mbar_wait(empty0 + 8 * s, ((it / kTcStages) - 1) & 1);
+                if (!ok) break;
+                const uint32_t a_dst = smem_u32(smem + s * kTcStageBytes), b_dst = a_dst + kTcATile;
+                mbar_expect_tx(full0 + 8 * s, kTcStageBytes);
+                tma_load_2d(a_dst, &map_a, ks * kTcBK, m0, full0 + 8 * s);
+                if (W_NK) {
+                    tma_load_2d(b_dst, &map_b, ks * kTcBK, n0, full0 + 8 * s);
+                } else {
 #pragma unroll
-                for (int c = 0; c < kTcBN / 64; c++)
-                    tma_load_2d(b_dst + c * kTcBChunk, &map_b, n0 + 64 * c, ks * kTcBK, full0 + 8 * s);
+                    for (int c = 0; c < kTcBN / 64; c++)
+                        tma_load_2d(b_dst + c * kTcBChunk, &map_b, n0 + 64 * c, ks * kTcBK, full0 + 8 * s);
+                }
             }
         }
     } else if (warp == 1 && lane == 0) {
         // instruction descriptor: D = f32, A = B = f16, A K-major, B MN-major unless W_NK, N = 256, M = 128
         const uint32_t idesc = (1u << 4) | ((W_NK ? 0u : 1u) << 16) | ((uint32_t)(kTcBN >> 3) << 17) | ((uint32_t)(kTcBM >> 4) << 24);
-        for (int ks = 0; ks < k_steps && ok; ks++) {
-            const int s = ks % kTcStages;
-            ok = mbar_wait(full0 + 8 * s, (ks / kTcStages) & 1);
+        int it = 0, lt = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, lt++) {
+            const int acc = lt & 1, use = lt >> 1;
+            // the accumulator must have been drained by the epilogue of the tile that used it before
+            if (use >= 1) ok = mbar_wait(acc_empty0 + 8 * acc, (use - 1) & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = smem_u32(smem + s * kTcStageBytes), b_addr = a_addr + kTcATile;
+            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * kTcBN);
+            for (int ks = 0; ks < k_steps; ks++, it++) {
+                const int s = it % kTcStages;
+                ok = mbar_wait(full0 + 8 * s, (it / kTcStages) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem + s * kTcStageBytes), b_addr = a_addr + kTcATile;
 #pragma unroll
-            for (int kk = 0; kk < kTcBK / 16; kk++) {
-                // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; 16 k = 32 bytes further in the row
-                const uint64_t adesc = umma_desc(a_addr + kk * 32, 16, 1024);
-                // B [N,K]: same form.  B [K,N]: MN-major, 64-column chunks 8192 bytes apart (LBO), 8-row k groups
-                // 1024 bytes apart (SBO); 16 k = two groups further
-                const uint64_t bdesc = W_NK ? umma_desc(b_addr + kk * 32, 16, 1024) : umma_desc(b_addr + kk * 2048, kTcBChunk, 1024);
-                umma_f16(tmem_base, adesc, bdesc, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kTcBK / 16; kk++) {
+                    // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; 16 k = 32 bytes further in the row
+                    const uint64_t adesc = umma_desc(a_addr + kk * 32, 16, 1024);
+                    // B [N,K]: same form.  B [K,N]: MN-major, 64-column chunks 8192 bytes apart (LBO), 8-row k groups
+                    // 1024 bytes apart (SBO); 16 k = two groups further
+                    const uint64_t bdesc = W_NK ? umma_desc(b_addr + kk * 32, 16, 1024) : umma_desc(b_addr + kk * 2048, kTcBChunk, 1024);
+                    umma_f16(tmem_d, adesc, bdesc, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
             }
-            umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
+            if (ok) umma_commit(acc_full0 + 8 * acc);  // the tile is complete when everything issued so far has run
         }
-        if (ok) umma_commit(accum_bar);
-    }
-    // epilogue: every warp reads its 32 accumulator rows (TMEM lanes 32*warp ..)
-    __syncwarp();
-    ok = mbar_wait(accum_bar, 0) && ok;
-    ok = __all_sync(0xffffffffu, ok);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    pdl_launch_dependents();
-    if (ok) {
-        const int row = m0 + warp * 32 + lane;
+        pdl_launch_dependents();
+    } else if (warp >= 2) {
+        // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31, which are the tile rows of the same numbers
+        const int q = warp & 3;
+        int lt = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, lt++) {
+            const int acc = lt & 1, use = lt >> 1;
+            int m0, n0;
+            tile_origin(t, m0, n0);
+            ok = mbar_wait(acc_full0 + 8 * acc, use & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + q * 32 + lane;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kTcBN; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row < M) {
-                __half* dst = y + (size_t)row * N + n0 + c0;
+            for (int c0 = 0; c0 < kTcBN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kTcBN + c0), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < M) {
+                    __half* dst = y + (size_t)row * N + n0 + c0;
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    if (n0 + c0 + 8 * j < N) {  // N is a multiple of 8
-                        uint32_t w[4];
+                    for (int j = 0; j < 4; j++) {
+                        if (n0 + c0 + 8 * j < N) {  // N is a multiple of 8
+                            uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const __half2 h = __floats2half2_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
-                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            for (int e = 0; e < 4; e++) {
+                                const __half2 h = __floats2half2_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+                                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                        *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
+            // this thread's reads of the accumulator are over: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(acc_empty0 + 8 * acc);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 2) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTcBN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * kTcBN) : "memory");
     }
 }
 
@@ -286,7 +324,7 @@ int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, in
     }
     const long tiles = (long)((N + kTcBN - 1) / kTcBN) * ((M + kTcBM - 1) / kTcBM);
     ONELLM_REQUIRE(tiles <= 0x7fffffffL, ONELLM_ERR_UNSUPPORTED, "gemm: too many tiles");
-    const dim3 grid((unsigned)tiles);
+    const dim3 grid((unsigned)std::min<long>(tiles, num_sms()));  // persistent: one block per SM (shared memory allows no more)
     if (nk)
         ONELLM_CUDA(launch_pdl(gemm_tc_kernel<true>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, y, M, N, K));
     else
