@@ -174,7 +174,9 @@ ONELLM_API int onellm_gemm_timeout_flag(void);
 /* Gate and up projections with SwiGLU applied on the way out:
  *     out[M,I] = silu(x.Wg) * (x.Wu),   Wg, Wu [K,I]
  * Replaces the gate GEMM, up GEMM and launchAct of LLaMAFFNLayer::forward
- * (src/layers/ffn/ffn.cpp:62-66, src/kernels/activation_kernel.cu:10-32).  F16 only. */
+ * (src/layers/ffn/ffn.cpp:62-66, src/kernels/activation_kernel.cu:10-32).  F16 only.  M <= 64: the
+ * weight-streaming kernel with both matrices in one ring; M > 64: tensor-core tiles whose 256 accumulator
+ * columns hold 128 gate columns beside the same 128 up columns, SwiGLU in the epilogue. */
 ONELLM_API int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, const void* Wu, void* out,
                                   int M, int I, int K, void* stream);
 

@@ -49,30 +49,6 @@ embedding_kernel(const int* __restrict__ ids, T* __restrict__ out, T* __restrict
     }
 }
 
-__global__ void __launch_bounds__(256)
-swiglu_pair_kernel(const __half* gate, const __half* up, __half* out, size_t nvec)
-{
-    pdl_launch_dependents();
-    pdl_wait();
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
-        float g[8], u[8], r[8];
-        Vec16<__half>::load(gate + i * 8, g);
-        Vec16<__half>::load(up + i * 8, u);
-#pragma unroll
-        for (int e = 0; e < 8; e++) r[e] = (g[e] / (1.0f + expf(-g[e]))) * u[e];
-        *reinterpret_cast<uint4*>(out + i * 8) = Vec16<__half>::pack(r);
-    }
-}
-
-int swiglu_pair_f16(const __half* gate, const __half* up, __half* out, size_t n, cudaStream_t st)
-{
-    ONELLM_REQUIRE(n % 8 == 0, ONELLM_ERR_ARG, "swiglu_pair: n must be a multiple of 8");
-    const size_t nvec = n / 8;
-    const int blocks = (int)((nvec + 255) / 256 < 2048 ? (nvec + 255) / 256 : 2048);
-    ONELLM_CUDA(launch_pdl(swiglu_pair_kernel, dim3(blocks), dim3(256), 0, st, gate, up, out, nvec));
-    return ONELLM_OK;
-}
-
 }  // namespace onellm
 
 using namespace onellm;

@@ -111,11 +111,17 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 // order (see below).  Warp 0 (one thread) is the TMA producer, warp 1 (one thread) issues the MMAs,
 // warps 2-5 are the epilogue.  Tensor memory holds TWO 128 x 256 accumulators, so the MMAs of the next
 // tile run while the epilogue warps drain the previous one.
-template <bool W_NK>
+// MODE 2: two [K,N] weights; the 256 accumulator columns of a tile are 128 columns of x.W (gate) beside the
+// same 128 columns of x.W2 (up), and the epilogue stores silu(gate) * up: the gate GEMM, the up GEMM and
+// launchAct of src/layers/ffn/ffn.cpp:62-66 in one pass, without the [T, 2, I] buffer.
+template <int MODE>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               __half* __restrict__ y, int M, int N, int K)
+               const __grid_constant__ CUtensorMap map_b2, __half* __restrict__ y, int M, int N, int K)
 {
+    constexpr bool W_NK = MODE == 1;
+    constexpr bool DUAL = MODE == 2;
+    constexpr int kOutN = DUAL ? kTcBN / 2 : kTcBN;  // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment for the 128-byte swizzle pattern
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -128,14 +134,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // tile to the right, so the tiles in flight at one time (one per SM) cover a near-square patch
     // of the output and share their A row blocks and B column blocks in L2.  (Row-major order made every
     // wave touch all column tiles of B: operands were read from DRAM seven times over.)
-    const int tiles_m = (M + kTcBM - 1) / kTcBM, tiles_n = (N + kTcBN - 1) / kTcBN;
+    const int tiles_m = (M + kTcBM - 1) / kTcBM, tiles_n = (N + kOutN - 1) / kOutN;
     const int n_tiles = tiles_m * tiles_n;
     auto tile_origin = [&](int t, int& m0, int& n0) {
         const int per_band = kTcBand * tiles_n;
         const int band = t / per_band, in_band = t % per_band;
         const int band_rows = min(kTcBand, tiles_m - band * kTcBand);
         m0 = (band * kTcBand + in_band % band_rows) * kTcBM;
-        n0 = (in_band / band_rows) * kTcBN;
+        n0 = (in_band / band_rows) * kOutN;
     };
     const int k_steps = (K + kTcBK - 1) / kTcBK;
 
@@ -178,6 +184,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tma_load_2d(a_dst, &map_a, ks * kTcBK, m0, full0 + 8 * s);
                 if (W_NK) {
                     tma_load_2d(b_dst, &map_b, ks * kTcBK, n0, full0 + 8 * s);
+                } else if (DUAL) {
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        tma_load_2d(b_dst + c * kTcBChunk, &map_b, n0 + 64 * c, ks * kTcBK, full0 + 8 * s);
+                        tma_load_2d(b_dst + (2 + c) * kTcBChunk, &map_b2, n0 + 64 * c, ks * kTcBK, full0 + 8 * s);
+                    }
                 } else {
 #pragma unroll
                     for (int c = 0; c < kTcBN / 64; c++)
@@ -232,10 +244,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + q * 32 + lane;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kTcBN; c0 += 32) {
+            for (int c0 = 0; c0 < kOutN; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kTcBN + c0), r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (DUAL) {
+                    uint32_t u[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kTcBN + kOutN + c0), u);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        const float g = __uint_as_float(r[i]);
+                        r[i] = __float_as_uint(g / (1.0f + __expf(-g)) * __uint_as_float(u[i]));
+                    }
+                } else {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                }
                 if (row < M) {
                     __half* dst = y + (size_t)row * N + n0 + c0;
 #pragma unroll
@@ -302,34 +325,53 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
 
 int gemm_f16_skinny(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout, cudaStream_t st);
 
-int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout, cudaStream_t st)
+// mode 0: W [K,N]; 1: W [N,K]; 2: W and W2 [K,N], y = silu(x.W) * (x.W2)
+static int gemm_tc_launch(const __half* x, const __half* W, const __half* W2, __half* y, int M, int N, int K, int mode, cudaStream_t st)
 {
     ONELLM_REQUIRE(K % 8 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED, "gemm: M > 64 needs K %% 8 == 0 and N %% 8 == 0 (K=%d N=%d)",
                    K, N);
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_b2;
     int rc = make_map(&map_a, x, (uint64_t)K, (uint64_t)M, kTcBM);
     if (rc) return rc;
-    const bool nk = w_layout == ONELLM_W_NK;
-    rc = nk ? make_map(&map_b, W, (uint64_t)K, (uint64_t)N, kTcBN) : make_map(&map_b, W, (uint64_t)N, (uint64_t)K, kTcBK);
+    rc = mode == 1 ? make_map(&map_b, W, (uint64_t)K, (uint64_t)N, kTcBN) : make_map(&map_b, W, (uint64_t)N, (uint64_t)K, kTcBK);
     if (rc) return rc;
-    static bool attr_set[2] = {false, false};
+    map_b2 = map_b;
+    if (mode == 2) {
+        rc = make_map(&map_b2, W2, (uint64_t)N, (uint64_t)K, kTcBK);
+        if (rc) return rc;
+    }
+    static bool attr_set[3] = {false, false, false};
     static std::mutex mu;
     {
         std::lock_guard<std::mutex> lock(mu);
-        if (!attr_set[nk]) {
-            ONELLM_CUDA(nk ? cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes)
-                           : cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
-            attr_set[nk] = true;
+        if (!attr_set[mode]) {
+            const void* fn = mode == 0 ? (const void*)gemm_tc_kernel<0> : mode == 1 ? (const void*)gemm_tc_kernel<1> : (const void*)gemm_tc_kernel<2>;
+            ONELLM_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
+            attr_set[mode] = true;
         }
     }
-    const long tiles = (long)((N + kTcBN - 1) / kTcBN) * ((M + kTcBM - 1) / kTcBM);
+    const int out_n = mode == 2 ? kTcBN / 2 : kTcBN;
+    const long tiles = (long)((N + out_n - 1) / out_n) * ((M + kTcBM - 1) / kTcBM);
     ONELLM_REQUIRE(tiles <= 0x7fffffffL, ONELLM_ERR_UNSUPPORTED, "gemm: too many tiles");
     const dim3 grid((unsigned)std::min<long>(tiles, num_sms()));  // persistent: one block per SM (shared memory allows no more)
-    if (nk)
-        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<true>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, y, M, N, K));
+    if (mode == 0)
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<0>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K));
+    else if (mode == 1)
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<1>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K));
     else
-        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<false>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, y, M, N, K));
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<2>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K));
     return ONELLM_OK;
+}
+
+int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout, cudaStream_t st)
+{
+    return gemm_tc_launch(x, W, nullptr, y, M, N, K, w_layout == ONELLM_W_NK ? 1 : 0, st);
+}
+
+// Gate and up projections with SwiGLU in the epilogue, M > 64.
+int gemm_swiglu_f16_large(const __half* x, const __half* Wg, const __half* Wu, __half* out, int M, int I, int K, cudaStream_t st)
+{
+    return gemm_tc_launch(x, Wg, Wu, out, M, I, K, 2, st);
 }
 
 // 1 when a tensor-core GEMM block gave up a bounded wait since the last call (and clears the flag).

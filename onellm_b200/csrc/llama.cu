@@ -156,7 +156,7 @@ struct Llama {
         *d_topk_id = nullptr, *d_bad_id = nullptr;
     unsigned char* d_finished = nullptr;
     float *d_topk_val = nullptr, *d_u = nullptr;
-    __half *res = nullptr, *y = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *act2 = nullptr,
+    __half *res = nullptr, *y = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr,
            *logits = nullptr;
     void* attn_ws = nullptr;
     size_t attn_ws_bytes = 0;
@@ -233,7 +233,6 @@ static void carve(Llama& m, Carver& cv)
     m.qkv = cv.take<__half>(B * m.qkv_cols);
     m.attn = cv.take<__half>(B * (size_t)m.Hl * D);
     m.act = cv.take<__half>(B * (size_t)m.Il);
-    m.act2 = cv.take<__half>(B * (size_t)m.Il);
     m.logits = cv.take<__half>(B * V);
     m.attn_ws_bytes = onellm_decode_attn_workspace_bytes((int)B, m.Hl, (int)D, c.max_seq_len);
     m.attn_ws = cv.take<char>(m.attn_ws_bytes);
@@ -241,8 +240,6 @@ static void carve(Llama& m, Carver& cv)
 
 static int blocks_for(size_t n) { return (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096); }
 
-// elementwise.cu: out = silu(gate) * up over n elements (n a multiple of 8); out may alias gate
-int swiglu_pair_f16(const __half* gate, const __half* up, __half* out, size_t n, cudaStream_t st);
 int embedding_launch(int dtype, const int* ids, void* out, void* out2, const void* table, int n_tokens, int hidden,
                      int vocab, int* bad_id_flag, bool pdl, cudaStream_t st);
 // sampling.cu
@@ -447,7 +444,7 @@ static int prefill_context(Llama& m, int B, int P, int history)
     cudaStream_t st = m.stream;
     void* sp = (void*)st;
     // scratch layout for T tokens
-    const size_t per_tok = ((size_t)2 * h + m.qkv_cols + (size_t)m.Hl * D + (size_t)2 * m.Il) * sizeof(__half);
+    const size_t per_tok = ((size_t)2 * h + m.qkv_cols + (size_t)m.Hl * D + (size_t)m.Il) * sizeof(__half);
     if (T > m.pf_tokens) {
         ONELLM_CUDA(cudaStreamSynchronize(st));
         if (m.pf_buf) cudaFree(m.pf_buf);
@@ -464,7 +461,6 @@ static int prefill_context(Llama& m, int B, int P, int history)
     __half* qkv = cv.take<__half>(T * m.qkv_cols);
     __half* attn = cv.take<__half>(T * (size_t)m.Hl * D);
     __half* act = cv.take<__half>(T * (size_t)m.Il);
-    __half* act2 = cv.take<__half>(T * (size_t)m.Il);
     int* d_cu = cv.take<int>(c.max_batch + 1);
     int* d_hist = cv.take<int>(c.max_batch);
     std::vector<int> cu(B + 1), hist(B, history);
@@ -490,18 +486,12 @@ static int prefill_context(Llama& m, int B, int P, int history)
         RC(onellm_gemm(ONELLM_F16, attn, L.wo, y, (int)T, h, m.Hl * D, ONELLM_W_KN, sp));
         RC(tp_allreduce(m, y, T * h));
         RC(onellm_add_residual_rmsnorm(ONELLM_F16, res, y, L.b_o, L.ffn_norm, c.rms_eps, (int)T, h, sp));
-        if (T <= 64) {
-            RC(onellm_gemm_swiglu(ONELLM_F16, y, L.w1, L.w3, act, (int)T, m.Il, h, sp));
-        } else {
-            RC(onellm_gemm(ONELLM_F16, y, L.w1, act, (int)T, m.Il, h, ONELLM_W_KN, sp));
-            RC(onellm_gemm(ONELLM_F16, y, L.w3, act2, (int)T, m.Il, h, ONELLM_W_KN, sp));
-            RC(swiglu_pair_f16(act, act2, act, T * m.Il, st));
-        }
+        RC(onellm_gemm_swiglu(ONELLM_F16, y, L.w1, L.w3, act, (int)T, m.Il, h, sp));  // SwiGLU in the epilogue at every M
         RC(onellm_gemm(ONELLM_F16, act, L.w2, y, (int)T, h, m.Il, ONELLM_W_KN, sp));
         RC(tp_allreduce(m, y, T * h));
         const __half* next_gamma = (l + 1 < c.num_layers) ? m.layers[l + 1].attn_norm : m.out_norm;
         RC(onellm_add_residual_rmsnorm(ONELLM_F16, res, y, nullptr, next_gamma, c.rms_eps, (int)T, h, sp));
-        m.launches += 10;
+        m.launches += 8;  // qkv, rope + cache write, attention, o, norm, gate/up + SwiGLU, down, norm
     }
     // last position of every sequence -> LM head, top-K, sampling (seeded with step = P, as the
     // position-by-position path does)

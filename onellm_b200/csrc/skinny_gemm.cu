@@ -192,6 +192,7 @@ static void skinny_nk_dispatch(const __half* x, const __half* W, __half* y, int 
 }
 
 // Defined in gemm_tc.cu: the tiled tensor-core path for M > 64.
+int gemm_swiglu_f16_large(const __half* x, const __half* Wg, const __half* Wu, __half* out, int M, int I, int K, cudaStream_t st);
 int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout,
                    cudaStream_t st);
 
@@ -275,12 +276,13 @@ extern "C" int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, cons
     ONELLM_REQUIRE(x && Wg && Wu && out, ONELLM_ERR_ARG, "gemm_swiglu: null pointer");
     ONELLM_REQUIRE(M >= 0 && I > 0 && K > 0, ONELLM_ERR_ARG, "gemm_swiglu: bad size");
     ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "gemm_swiglu: only F16 is implemented");
-    ONELLM_REQUIRE(M <= 64, ONELLM_ERR_UNSUPPORTED,
-                   "gemm_swiglu: fused path covers M <= 64; use two projections and onellm_swiglu");
     ONELLM_REQUIRE(K % 16 == 0 && I % 8 == 0, ONELLM_ERR_UNSUPPORTED, "gemm_swiglu: need K %% 16 == 0, I %% 8 == 0");
     ONELLM_REQUIRE(aligned16(x) && aligned16(Wg) && aligned16(Wu) && aligned16(out), ONELLM_ERR_ARG,
                    "gemm_swiglu: pointers must be 16-byte aligned");
     if (M == 0) return ONELLM_OK;
+    if (M > 64)  // tensor-core tiles, SwiGLU in the epilogue
+        return gemm_swiglu_f16_large((const __half*)x, (const __half*)Wg, (const __half*)Wu, (__half*)out, M, I, K,
+                                     reinterpret_cast<cudaStream_t>(stream));
     ONELLM_CUDA(skinny_kn_dispatch((const __half*)x, (const __half*)Wg, (const __half*)Wu, (__half*)out, M, I, K,
                                    true, reinterpret_cast<cudaStream_t>(stream)));
     return ONELLM_OK;

@@ -236,6 +236,21 @@ def test_gemm_swiglu_fused(ob, cuda, orc, M, I, K):
     assert rel_err(out.float().cpu().numpy(), ref) < TOL["f16"]
 
 
+@pytest.mark.parametrize("M,I,K", [(128, 256, 64), (65, 1376, 4096), (300, 11008, 4096), (1024, 11008, 4096), (200, 1000, 528)])
+def test_gemm_swiglu_tensor_core_tiles(ob, cuda, orc, M, I, K):
+    """M > 64: gate and up share one tcgen05 tile (128 + 128 accumulator columns), SwiGLU in the epilogue; ragged M, I, K."""
+    torch = cuda
+    rng = np.random.default_rng(I + M)
+    x = _round(rng.standard_normal((M, K)), "f16")
+    Wg, Wu = _round(0.02 * rng.standard_normal((K, I)), "f16"), _round(0.02 * rng.standard_normal((K, I)), "f16")
+    out = torch.full((M + 1, I), 7.0, device="cuda", dtype=torch.float16)   # one guard row behind the output
+    ob.gemm_swiglu(ob.F16, _dev(torch, x, "f16"), _dev(torch, Wg, "f16"), _dev(torch, Wu, "f16"), out, M, I, K)
+    ref = orc.swiglu2(orc.gemm(x, Wg), orc.gemm(x, Wu))
+    assert rel_err(out[:M].float().cpu().numpy(), ref) < TOL["f16"]
+    assert float(out[M].float().min()) == 7.0 and float(out[M].float().max()) == 7.0
+    assert ob.lib().onellm_gemm_timeout_flag() == 0
+
+
 @pytest.mark.parametrize("dt", ["f16", "f32"])
 def test_swiglu_standalone(ob, cuda, orc, dt):
     torch = cuda
