@@ -83,6 +83,68 @@ qkv_rope_kvcache_kernel(T* __restrict__ qkv, const T* __restrict__ bias, const i
     }
 }
 
+// The same with 16-byte accesses and one sincosf per (token, pair) instead of one per (token, head, pair):
+// the angles of a token are shared by all its heads, and sincosf on arguments of thousands of radians is
+// the slow path of the math library.  Needs D, the cache strides and all pointers aligned to 16 bytes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_rope_kvcache_vec_kernel(T* __restrict__ qkv, const T* __restrict__ bias, const int* __restrict__ cu_seqlens,
+                            const int* __restrict__ history, T* __restrict__ k_cache, T* __restrict__ v_cache, long cs_b,
+                            long cs_h, long cs_s, int B, int H, int Hkv, int D, int rot_dim, int max_seq, const RopeTable rt,
+                            int* __restrict__ overflow_flag)
+{
+    constexpr int N = Vec16<T>::N;
+    __shared__ float s_sin[kMaxPairs], s_cos[kMaxPairs];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int b, i;
+    locate_token(cu_seqlens, B, t, b, i);
+    const int pos = history[b] + i;
+    if (pos >= max_seq) {  // the cache has no such row: record it, leave q alone
+        if (threadIdx.x == 0 && overflow_flag) atomicExch(overflow_flag, 1);
+        return;
+    }
+    const int QH = H + 2 * Hkv, half_d = D / 2;
+    for (int pr = threadIdx.x; pr < half_d; pr += blockDim.x) {
+        float sn = 0.f, cs = 1.f;  // pairs beyond the rotary dimension pass through
+        if (2 * pr < rot_dim) sincosf((float)pos / rt.denom[pr], &sn, &cs);
+        s_sin[pr] = sn;
+        s_cos[pr] = cs;
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)t * QH * D;
+    const int vec_per_head = D / N;
+    for (int idx = threadIdx.x; idx < QH * vec_per_head; idx += blockDim.x) {
+        const int head = idx / vec_per_head, e0 = (idx % vec_per_head) * N;
+        float f[N];
+        Vec16<T>::load(row + head * D + e0, f);
+        if (bias) {
+            float bb[N];
+            Vec16<T>::load(bias + head * D + e0, bb);
+#pragma unroll
+            for (int e = 0; e < N; e++) f[e] += bb[e];
+        }
+        if (head < H + Hkv) {  // q and k heads rotate, v heads do not
+#pragma unroll
+            for (int p = 0; p < N / 2; p++) {
+                const float cs = s_cos[e0 / 2 + p], sn = s_sin[e0 / 2 + p];
+                const float x = f[2 * p], y = f[2 * p + 1];
+                f[2 * p] = cs * x - sn * y;
+                f[2 * p + 1] = cs * y + sn * x;
+            }
+        }
+        T* dst;
+        if (head < H) {
+            dst = row + head * D + e0;
+        } else {
+            const int hk = head < H + Hkv ? head - H : head - H - Hkv;
+            dst = (head < H + Hkv ? k_cache : v_cache) + b * cs_b + hk * cs_h + (long)pos * cs_s + e0;
+        }
+        *reinterpret_cast<uint4*>(dst) = Vec16<T>::pack(f);
+    }
+}
+
 // ---- causal attention over the cache, fp16, D = 64 or 128 ---------------------------------------------
 constexpr int kCtxQ = 64;    // query rows per block (4 warps x 16)
 constexpr int kCtxKV = 64;   // cache rows per tile
@@ -281,14 +343,17 @@ extern "C" int onellm_qkv_bias_rope_kvcache(int dtype, void* qkv, const void* bi
     fill_rope(rt, rot_dim < D ? rot_dim : D, rope_base);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int rd = rot_dim < D ? rot_dim : D;
+    const long vec = dtype == ONELLM_F16 ? 8 : 4;  // elements per 16 bytes
+    const bool aligned = D % vec == 0 && cs_b % vec == 0 && cs_h % vec == 0 && cs_s % vec == 0 && aligned16(qkv) && aligned16(k_cache) &&
+                         aligned16(v_cache) && (!bias || aligned16(bias));
     if (dtype == ONELLM_F16)
-        ONELLM_CUDA(launch_pdl(qkv_rope_kvcache_kernel<__half>, dim3(num_tokens), dim3(256), 0, st, (__half*)qkv,
-                               (const __half*)bias, cu_seqlens, history_length, (__half*)k_cache, (__half*)v_cache, cs_b, cs_h,
-                               cs_s, B, H, Hkv, D, rd, max_seq_len, rt, overflow_flag));
+        ONELLM_CUDA(launch_pdl(aligned ? qkv_rope_kvcache_vec_kernel<__half> : qkv_rope_kvcache_kernel<__half>, dim3(num_tokens), dim3(256), 0,
+                               st, (__half*)qkv, (const __half*)bias, cu_seqlens, history_length, (__half*)k_cache, (__half*)v_cache,
+                               cs_b, cs_h, cs_s, B, H, Hkv, D, rd, max_seq_len, rt, overflow_flag));
     else
-        ONELLM_CUDA(launch_pdl(qkv_rope_kvcache_kernel<float>, dim3(num_tokens), dim3(256), 0, st, (float*)qkv,
-                               (const float*)bias, cu_seqlens, history_length, (float*)k_cache, (float*)v_cache, cs_b, cs_h,
-                               cs_s, B, H, Hkv, D, rd, max_seq_len, rt, overflow_flag));
+        ONELLM_CUDA(launch_pdl(aligned ? qkv_rope_kvcache_vec_kernel<float> : qkv_rope_kvcache_kernel<float>, dim3(num_tokens), dim3(256), 0,
+                               st, (float*)qkv, (const float*)bias, cu_seqlens, history_length, (float*)k_cache, (float*)v_cache, cs_b,
+                               cs_h, cs_s, B, H, Hkv, D, rd, max_seq_len, rt, overflow_flag));
     return ONELLM_OK;
 }
 
