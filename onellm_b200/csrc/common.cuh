@@ -11,6 +11,9 @@ namespace onellm {
 
 // Thread-local text of the last failure, returned by onellm_last_error().
 void set_error(const char* fmt, ...);
+// Every kernel launch of the library is counted per host thread (launch_pdl does it itself).
+void note_launch(int n = 1);
+long launches_noted();
 
 #define ONELLM_REQUIRE(cond, code, ...)          \
     do {                                         \
@@ -166,6 +169,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    note_launch();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

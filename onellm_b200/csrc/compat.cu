@@ -207,6 +207,7 @@ using namespace onellm;
 
 #define DISPATCH(dtype, who, F16_CALL, F32_CALL)                                   \
     do {                                                                           \
+        note_launch();                                                             \
         if ((dtype) == ONELLM_F16) { F16_CALL; }                                   \
         else if ((dtype) == ONELLM_F32) { F32_CALL; }                              \
         else ONELLM_REQUIRE(false, ONELLM_ERR_UNSUPPORTED, who ": dtype %d", dtype); \
@@ -221,6 +222,7 @@ extern "C" int onellm_cal_padding_offset(int* padding_offset, int* cum_seqlens, 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     int* d_total = nullptr;
     if (host_token_num) ONELLM_CUDA(cudaMallocAsync(&d_total, sizeof(int), st));
+    note_launch();
     padding_offset_kernel<<<1, 256, 0, st>>>(padding_offset, cum_seqlens, seq_lens, B, max_q_len, d_total);
     ONELLM_CHECK_LAUNCH();
     if (host_token_num) {

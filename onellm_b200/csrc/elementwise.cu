@@ -66,6 +66,7 @@ extern "C" int onellm_swiglu(int dtype, const void* input, void* out, int tokens
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int nvec = inter / (int)(16 / es);
     const dim3 grid((nvec + 255) / 256, tokens);
+    note_launch();
     if (dtype == ONELLM_F16)
         swiglu_kernel<__half><<<grid, 256, 0, st>>>((const __half*)input, (__half*)out, inter);
     else
@@ -87,6 +88,7 @@ int embedding_launch(int dtype, const int* ids, void* out, void* out2, const voi
     ONELLM_REQUIRE(((size_t)hidden * es) % 16 == 0 && aligned16(out) && aligned16(table) && (!out2 || aligned16(out2)),
                    ONELLM_ERR_ARG, "embedding: rows must be 16-byte aligned");
     if (n_tokens == 0) return ONELLM_OK;
+    if (!pdl) note_launch();  // launch_pdl counts its own
     if (dtype == ONELLM_F16) {
         if (pdl)
             ONELLM_CUDA(launch_pdl(embedding_kernel<__half>, dim3(n_tokens), dim3(256), 0, st, ids, (__half*)out,

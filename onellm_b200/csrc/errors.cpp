@@ -1,4 +1,4 @@
-// Thread-local error text behind onellm_last_error().
+// Thread-local error text behind onellm_last_error(), and the per-thread count of kernel launches.
 #include <stdarg.h>
 #include <stdio.h>
 
@@ -15,6 +15,12 @@ void set_error(const char* fmt, ...)
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
 }
+
+// Kernel launches issued by the calling thread through this library (the model reports them:
+// onellm_llama_get_state).
+static thread_local long g_launches = 0;
+void note_launch(int n) { g_launches += n; }
+long launches_noted() { return g_launches; }
 
 }  // namespace onellm
 

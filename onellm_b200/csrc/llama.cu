@@ -262,7 +262,7 @@ static int tp_allreduce(Llama& m, __half* buf, size_t n)
     const ncclResult_t r = nccl_api().AllReduce(buf, buf, n, ncclHalf, ncclSum, m.comm, m.stream);
     ONELLM_REQUIRE(r == ncclSuccess, ONELLM_ERR_COMM, "ncclAllReduce: %s",
                    nccl_api().GetErrorString ? nccl_api().GetErrorString(r) : "error");
-    m.launches++;
+    note_launch();
     return ONELLM_OK;
 }
 
@@ -277,10 +277,11 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
     // The step counter advances first.  This kernel, the id gather and the embedding are
     // launched with full stream dependencies; every later kernel of the step may overlap its
     // predecessor's tail (programmatic dependent launch) and therefore starts after these.
+    note_launch();
     advance_step_kernel<<<1, 1, 0, st>>>(m.d_step);
     if (mode & MODE_GATHER) {
+        note_launch();
         gather_prompt_ids_kernel<<<(B + 127) / 128, 128, 0, st>>>(m.d_prompt, prompt_len, m.d_step, m.d_ids, B);
-        m.launches++;
     }
     const long cs_b = (long)m.Hkvl * c.max_seq_len * D, cs_h = (long)c.max_seq_len * D, cs_s = D;
     const float scale = 1.0f / sqrtf((float)D);
@@ -303,7 +304,6 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         // that follows a norm reads it raw and scales by rsqrt(mean(x^2) + eps) on the way out (the
         // norm's gamma is already inside its weights), o_proj and down_proj add their result to it.
         RC(embedding_launch(ONELLM_F16, m.d_ids, m.res, nullptr, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
-        m.launches += 2;
         for (int l = 0; l < c.num_layers; l++) {
             const LayerW& L = m.layers[l];
             RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w_qkv, nullptr, m.qkv, B, m.qkv_cols, h, c.rms_eps, nullptr, nullptr, sp));
@@ -311,11 +311,9 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
             RC(onellm_gemm_fused(ONELLM_F16, m.attn, L.wo, nullptr, m.res, B, h, m.Hl * D, -1.f, m.res, L.b_o, sp));
             RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w1, L.w3, m.act, B, m.Il, h, c.rms_eps, nullptr, nullptr, sp));
             RC(onellm_gemm_fused(ONELLM_F16, m.act, L.w2, nullptr, m.res, B, h, m.Il, -1.f, m.res, nullptr, sp));
-            m.launches += 6;  // qkv, attention + combine, o, gate/up, down
         }
         if (mode & MODE_HEAD) {
             RC(onellm_rmsnorm(ONELLM_F16, m.res, m.out_norm, c.rms_eps, B, h, sp));  // in place: the stream ends here
-            m.launches += 1;
         }
         head_in = m.res;
     } else if (m.p2p_connected) {
@@ -325,7 +323,6 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         __half* send0 = static_cast<__half*>(onellm_p2p_send_buffer(m.p2p, 0));
         __half* send1 = static_cast<__half*>(onellm_p2p_send_buffer(m.p2p, 1));
         RC(embedding_launch(ONELLM_F16, m.d_ids, m.res, nullptr, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
-        m.launches += 2;
         for (int l = 0; l < c.num_layers; l++) {
             const LayerW& L = m.layers[l];
             RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w_qkv, nullptr, m.qkv, B, m.qkv_cols, h, c.rms_eps, nullptr, nullptr, sp));
@@ -335,11 +332,9 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
             RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w1, L.w3, m.act, B, m.Il, h, c.rms_eps, nullptr, nullptr, sp));
             RC(onellm_gemm_fused(ONELLM_F16, m.act, L.w2, nullptr, send1, B, h, m.Il, -1.f, nullptr, nullptr, sp));
             RC(onellm_p2p_allreduce_add(m.p2p, ONELLM_F16, 1, m.res, nullptr, B * h, h, sp));
-            m.launches += 8;  // qkv, attention + combine, o, sum, gate/up, down, sum
         }
         if (mode & MODE_HEAD) {
             RC(onellm_rmsnorm(ONELLM_F16, m.res, m.out_norm, c.rms_eps, B, h, sp));
-            m.launches += 1;
         }
         head_in = m.res;
     } else {
@@ -347,7 +342,6 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         // add, so the norm kernels stay (their per-layer gamma is all ones after finalize_weights)
         RC(embedding_launch(ONELLM_F16, m.d_ids, m.y, m.res, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
         RC(onellm_rmsnorm(ONELLM_F16, m.y, m.layers[0].attn_norm, c.rms_eps, B, h, sp));
-        m.launches += 3;
         for (int l = 0; l < c.num_layers; l++) {
             const LayerW& L = m.layers[l];
             RC(onellm_gemm(ONELLM_F16, m.y, L.w_qkv, m.qkv, B, m.qkv_cols, h, ONELLM_W_KN, sp));
@@ -360,7 +354,6 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
             RC(tp_allreduce(m, m.y, (size_t)B * h));
             const __half* next_gamma = (l + 1 < c.num_layers) ? m.layers[l + 1].attn_norm : m.out_norm;
             RC(onellm_add_residual_rmsnorm(ONELLM_F16, m.res, m.y, nullptr, next_gamma, c.rms_eps, B, h, sp));
-            m.launches += 8;  // qkv, attention + combine, o, norm, gate/up, down, norm
         }
     }
     if (mode & MODE_HEAD) {
@@ -368,7 +361,6 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
         RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size,
                               c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
-        m.launches += 3;
     }
     ONELLM_CHECK_LAUNCH();
     return ONELLM_OK;
@@ -391,7 +383,9 @@ static int run_step(Llama& m, int mode, int prompt_len)
     int bound = (step + 255) / 256 * 256;
     if (bound > m.c.max_seq_len) bound = m.c.max_seq_len;
     if (!m.use_graphs) {
+        const long before = launches_noted();
         RC(enqueue_step(m, mode, bound, prompt_len));
+        m.launches += launches_noted() - before;
         m.cur_len++;
         return ONELLM_OK;
     }
@@ -402,12 +396,14 @@ static int run_step(Llama& m, int mode, int prompt_len)
         // first step of this shape runs eagerly: the launch planners query occupancy and set
         // function attributes once per kernel, which must not happen inside a stream capture
         m.warmed[key] = 1;
+        const long before = launches_noted();
         RC(enqueue_step(m, mode, bound, prompt_len));
+        m.launches += launches_noted() - before;
         m.cur_len++;
         return ONELLM_OK;
     }
     if (it == m.graphs.end()) {
-        const long before = m.launches;
+        const long before = launches_noted();  // what the capture records = the nodes of one replay
         cudaGraph_t g = nullptr;
         ONELLM_CUDA(cudaStreamBeginCapture(m.stream, cudaStreamCaptureModeThreadLocal));
         const int rc = enqueue_step(m, mode, bound, prompt_len);
@@ -421,8 +417,7 @@ static int run_step(Llama& m, int mode, int prompt_len)
         const cudaError_t e2 = cudaGraphInstantiate(&ge, g, 0);
         cudaGraphDestroy(g);
         ONELLM_REQUIRE(e2 == cudaSuccess, ONELLM_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e2));
-        m.graph_nodes[key] = (int)(m.launches - before);
-        m.launches = before;
+        m.graph_nodes[key] = (int)(launches_noted() - before);
         it = m.graphs.emplace(key, ge).first;
     }
     ONELLM_CUDA(cudaGraphLaunch(it->second, m.stream));
@@ -469,6 +464,7 @@ static int prefill_context(Llama& m, int B, int P, int history)
     ONELLM_CUDA(cudaMemcpyAsync(d_hist, hist.data(), B * sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaStreamSynchronize(st));  // cu / hist live on this stack frame
 
+    const long launches_before = launches_noted();
     // d_prompt is [B, P] row-major = the packed token order
     RC(embedding_launch(ONELLM_F16, m.d_prompt, y, res, m.tok_emb, (int)T, h, c.vocab_size, m.d_bad_id, false, st));
     RC(onellm_rmsnorm(ONELLM_F16, y, m.layers[0].attn_norm, c.rms_eps, (int)T, h, sp));
@@ -491,7 +487,6 @@ static int prefill_context(Llama& m, int B, int P, int history)
         RC(tp_allreduce(m, y, T * h));
         const __half* next_gamma = (l + 1 < c.num_layers) ? m.layers[l + 1].attn_norm : m.out_norm;
         RC(onellm_add_residual_rmsnorm(ONELLM_F16, res, y, nullptr, next_gamma, c.rms_eps, (int)T, h, sp));
-        m.launches += 8;  // qkv, rope + cache write, attention, o, norm, gate/up + SwiGLU, down, norm
     }
     // last position of every sequence -> LM head, top-K, sampling (seeded with step = P, as the
     // position-by-position path does)
@@ -501,7 +496,7 @@ static int prefill_context(Llama& m, int B, int P, int history)
     RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
     RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
                           m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
-    m.launches += 5;
+    m.launches += launches_noted() - launches_before;
     m.cur_len = history + P;
     return ONELLM_OK;
 }

@@ -4,20 +4,23 @@
 // 64 KB at batch 8) are summed over the ranks and added to the residual stream
 // (src/layers/decoder/self_decoder.cpp:50-73 of the reference run under tensor parallelism).  A
 // library all-reduce costs ten to twenty microseconds of latency for such a message, twice per layer.
-// Here every rank keeps its partial in a buffer the other ranks can map (CUDA IPC over NVLink /
-// NVSwitch), tells them with one flag store per peer that it is complete, and then reads all the
-// partials itself with plain peer loads, adds them in rank order (every rank gets bit-identical sums)
-// together with the residual and the bias, and writes only its own copy of the residual stream:
+// Here every rank owns receive buffers the other ranks can map (CUDA IPC over NVLink / NVSwitch).
+// One kernel per call: each rank PUSHES its partial into its slot of every peer's receive buffer with
+// plain peer stores, then waits for the peers' partials to arrive in its own memory, adds them in rank
+// order (every rank gets bit-identical sums) together with the residual and the bias, and writes only
+// its own copy of the residual stream:
 //
 //     residual <- residual + bias + sum_r partial_r
 //
-// Synchronisation is per thread block and needs no cross-block state: block b of rank r owns a
-// sequence counter, stores it into slot [b][r] of every peer's flag array and waits until its own
-// slots [b][0..world) have reached it.  Two send buffers are used in turn (o_proj, down_proj); a rank
-// can only overwrite a buffer two calls later, after every peer has announced the call in between,
-// which it does only once its reads of the earlier call are over.  Every wait is bounded: when it
-// runs out the block sets the error word of its rank and carries on with whatever the peers' buffers
-// hold, so the kernel always ends.
+// There are no flags and no fences: every 8-byte word that crosses the link is {two fp16 values, the
+// call's sequence number}, written with one store, so a word is valid exactly when its sequence number
+// is the one the receiver expects (the receiver polls the data itself; the cost of a call is one
+// one-way store latency instead of a flag round plus a load round trip).  Sequence numbers are per
+// thread block (block b of every rank pairs with block b of the others), so there is no cross-block
+// state.  Two receive buffers are used in turn (o_proj, down_proj): a rank can only overwrite a slot two
+// calls later, after the owner has pushed the call in between, which it does only once its reads of the
+// earlier call are over.  Every wait is bounded: when it runs out the block sets the error word of its
+// rank and carries on with whatever the buffers hold, so the kernel always ends.
 //
 // No multicast, no multimem: plain loads and stores on mapped peer memory.
 #include <string.h>
@@ -29,16 +32,17 @@
 namespace onellm {
 
 constexpr int kP2pMaxWorld = 8;
-constexpr int kP2pMaxBlocks = 64;
+constexpr int kP2pMaxBlocks = 128;
 constexpr int kP2pThreads = 256;
-constexpr int kP2pVecPerThread = 4;                       // 16-byte vectors per thread
+constexpr int kP2pVecPerThread = 2;                       // 16-byte vectors per thread
 constexpr long long kP2pWaitCycles = 2000LL * 1000 * 1000;  // a wait for a peer gives up after about a second of SM clocks
 
 // Layout of the block every rank allocates and exports:
-//   [0]            control: flags[kP2pMaxBlocks][kP2pMaxWorld] (written by peers), counters[kP2pMaxBlocks], error
-//   [kCtlBytes]    send buffer 0, send buffer 1 (max_elems halfs each)
+//   [0]            control: counters[kP2pMaxBlocks] (sequence number per thread block), error
+//   [kCtlBytes]    send buffer 0, send buffer 1 (max_elems halfs each; written by this rank's projections)
+//   [..]           receive buffers [2][world][max_elems / 2] of 8-byte words {half2 data, sequence number},
+//                  slot [which][r] written by rank r
 struct P2pControl {
-    int flags[kP2pMaxBlocks][kP2pMaxWorld];
     int counters[kP2pMaxBlocks];
     int error;
     int pad[63];
@@ -46,21 +50,13 @@ struct P2pControl {
 constexpr size_t kCtlBytes = (sizeof(P2pControl) + 255) / 256 * 256;
 
 struct P2pPeers {
-    const __half* data[kP2pMaxWorld];  // send buffer of this call on every rank (own included)
-    P2pControl* ctl[kP2pMaxWorld];     // control block of every rank (own included)
+    uint2* recv[kP2pMaxWorld];  // this rank's slot [which][rank] in the receive buffer of every rank (own entry unused)
 };
 
-__device__ __forceinline__ void st_relaxed_sys(int* p, int v) { asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ int ld_relaxed_sys(const int* p)
+__device__ __forceinline__ void st_relaxed_sys_16(void* p, uint4 v)
 {
-    int v;
-    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-__device__ __forceinline__ void fence_acquire_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
-
-// peer data is read once per call, after the acquire on the peer's flag: a system-scope load that
-// bypasses the non-coherent path
 __device__ __forceinline__ uint4 ld_relaxed_sys_16(const void* p)
 {
     uint4 r;
@@ -68,48 +64,72 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_16(const void* p)
     return r;
 }
 
+// send: this rank's partial (local); my_recv: this rank's receive buffer of this call, [world][slot_words] words.
 __global__ void __launch_bounds__(kP2pThreads)
-p2p_allreduce_add_kernel(const P2pPeers peers, int rank, int world, __half* __restrict__ resid, const __half* __restrict__ bias,
-                         int n_elems, int row_len)
+p2p_allreduce_add_kernel(const P2pPeers peers, P2pControl* __restrict__ ctl, const __half* __restrict__ send,
+                         const uint2* __restrict__ my_recv, size_t slot_words, int rank, int world, __half* __restrict__ resid,
+                         const __half* __restrict__ bias, int n_elems, int row_len)
 {
     __shared__ int s_seq;
     pdl_launch_dependents();
-    pdl_wait();  // the projection that wrote this rank's partial has completed and its stores are visible
-    P2pControl* mine = peers.ctl[rank];
+    pdl_wait();  // the projection that wrote this rank's partial has completed
     const int b = blockIdx.x;
     if (threadIdx.x == 0) {
-        const int seq = mine->counters[b] + 1;
-        mine->counters[b] = seq;
+        const int seq = ctl->counters[b] + 1;
+        ctl->counters[b] = seq;
         s_seq = seq;
     }
     __syncthreads();
-    const int seq = s_seq;
-    if (threadIdx.x < world) {
-        const int p = threadIdx.x;
-        // "partial number seq of rank `rank` is complete".  No release fence is needed in front of the store:
-        // the partial was written by the kernel before this one, whose completion (griddepcontrol.wait above)
-        // has already made it visible at system scope.
-        st_relaxed_sys(&peers.ctl[p]->flags[b][rank], seq);
-        const long long t0 = clock64();  // the SM's own cycle counter: reading it costs nothing next to the poll
-        while (ld_relaxed_sys(&mine->flags[b][p]) < seq) {
-            if (clock64() - t0 > kP2pWaitCycles) {
-                atomicExch(&mine->error, 1);
-                break;
-            }
-        }
-        fence_acquire_sys();  // the peer's partial is read only after its flag has been seen
-    }
-    __syncthreads();
-    const int n_vec = n_elems / 8;
+    const uint32_t seq = (uint32_t)s_seq;
+    const int n_vec = n_elems / 8;           // 16 bytes of fp16 = 4 words on the wire
     const int v0 = (b * kP2pThreads + threadIdx.x) * kP2pVecPerThread;
+
+    // 1. push: {d0, seq, d1, seq} {d2, seq, d3, seq} per 16 bytes of the partial, to every peer
+    uint4 own[kP2pVecPerThread];
+#pragma unroll
+    for (int j = 0; j < kP2pVecPerThread; j++) {
+        own[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (v0 + j < n_vec) own[j] = *reinterpret_cast<const uint4*>(send + (size_t)(v0 + j) * 8);
+    }
+#pragma unroll
+    for (int r = 0; r < kP2pMaxWorld; r++)
+        if (r < world && r != rank) {
+#pragma unroll
+            for (int j = 0; j < kP2pVecPerThread; j++)
+                if (v0 + j < n_vec) {
+                    uint2* dst = peers.recv[r] + (size_t)(v0 + j) * 4;
+                    st_relaxed_sys_16(dst, make_uint4(own[j].x, seq, own[j].y, seq));
+                    st_relaxed_sys_16(dst + 2, make_uint4(own[j].z, seq, own[j].w, seq));
+                }
+        }
+
+    // 2. collect: a word of a peer is there when it carries this call's sequence number
     uint4 part[kP2pMaxWorld][kP2pVecPerThread];
+    const long long t0 = clock64();  // the SM's own cycle counter bounds the wait
+    bool gave_up = false;
 #pragma unroll
     for (int r = 0; r < kP2pMaxWorld; r++)
         if (r < world) {
 #pragma unroll
-            for (int j = 0; j < kP2pVecPerThread; j++)
-                if (v0 + j < n_vec) part[r][j] = ld_relaxed_sys_16(peers.data[r] + (size_t)(v0 + j) * 8);
+            for (int j = 0; j < kP2pVecPerThread; j++) {
+                part[r][j] = own[j];
+                if (r == rank || v0 + j >= n_vec) continue;
+                const uint2* src = my_recv + (size_t)r * slot_words + (size_t)(v0 + j) * 4;
+                uint4 lo, hi;
+                for (;;) {
+                    lo = ld_relaxed_sys_16(src);
+                    hi = ld_relaxed_sys_16(src + 2);
+                    if ((lo.y == seq && lo.w == seq && hi.y == seq && hi.w == seq) || gave_up) break;
+                    if (clock64() - t0 > kP2pWaitCycles) {
+                        atomicExch(&ctl->error, 1);
+                        gave_up = true;
+                    }
+                }
+                part[r][j] = make_uint4(lo.x, lo.z, hi.x, hi.z);
+            }
         }
+
+    // 3. sum in rank order, add residual and bias, store
 #pragma unroll
     for (int j = 0; j < kP2pVecPerThread; j++) {
         const int v = v0 + j;
@@ -137,6 +157,14 @@ p2p_allreduce_add_kernel(const P2pPeers peers, int rank, int world, __half* __re
 struct P2pComm {
     int rank = 0, world = 1, device = 0;
     size_t max_elems = 0, block_bytes = 0;
+    size_t send_bytes() const { return (max_elems * sizeof(__half) + 255) / 256 * 256; }
+    size_t slot_words() const { return max_elems / 2; }
+    // receive slot [which][src] inside the block that starts at `base`
+    uint2* recv_slot(void* base, int which, int src) const
+    {
+        return reinterpret_cast<uint2*>(static_cast<char*>(base) + kCtlBytes + 2 * send_bytes()) +
+               ((size_t)which * world + src) * slot_words();
+    }
     void* local = nullptr;                    // this rank's block
     void* mapped[kP2pMaxWorld] = {};          // every rank's block in this process's address space
     bool connected = false;
@@ -159,7 +187,7 @@ extern "C" int onellm_p2p_create(int rank, int world, size_t max_elems, onellm_p
     c->rank = rank;
     c->world = world;
     c->max_elems = max_elems;
-    c->block_bytes = kCtlBytes + 2 * ((max_elems * sizeof(__half) + 255) / 256 * 256);
+    c->block_bytes = kCtlBytes + 2 * c->send_bytes() + (size_t)2 * world * c->slot_words() * sizeof(uint2);
     cudaError_t e = cudaGetDevice(&c->device);
     if (e == cudaSuccess) e = cudaMalloc(&c->local, c->block_bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->block_bytes);
@@ -206,8 +234,7 @@ extern "C" void* onellm_p2p_send_buffer(onellm_p2p* h, int which)
 {
     P2pComm* c = reinterpret_cast<P2pComm*>(h);
     if (!c || which < 0 || which > 1) return nullptr;
-    const size_t buf_bytes = (c->max_elems * sizeof(__half) + 255) / 256 * 256;
-    return static_cast<char*>(c->local) + kCtlBytes + (size_t)which * buf_bytes;
+    return static_cast<char*>(c->local) + kCtlBytes + (size_t)which * c->send_bytes();
 }
 
 extern "C" int onellm_p2p_allreduce_add(onellm_p2p* h, int dtype, int which, void* resid, const void* bias, int n_elems, int row_len,
@@ -224,15 +251,13 @@ extern "C" int onellm_p2p_allreduce_add(onellm_p2p* h, int dtype, int which, voi
                    row_len, c->max_elems);
     ONELLM_REQUIRE(aligned16(resid) && (!bias || aligned16(bias)), ONELLM_ERR_ARG, "p2p_allreduce_add: pointers must be 16-byte aligned");
     P2pPeers peers = {};
-    const size_t buf_bytes = (c->max_elems * sizeof(__half) + 255) / 256 * 256;
-    for (int r = 0; r < c->world; r++) {
-        peers.ctl[r] = static_cast<P2pControl*>(c->mapped[r]);
-        peers.data[r] = reinterpret_cast<const __half*>(static_cast<const char*>(c->mapped[r]) + kCtlBytes + (size_t)which * buf_bytes);
-    }
+    for (int r = 0; r < c->world; r++) peers.recv[r] = c->recv_slot(c->mapped[r], which, c->rank);  // my slot on rank r
     const int per_block = kP2pThreads * kP2pVecPerThread * 8;
     const int blocks = (n_elems + per_block - 1) / per_block;  // the same on every rank: blocks pair up by index
     ONELLM_CUDA(launch_pdl(p2p_allreduce_add_kernel, dim3(blocks), dim3(kP2pThreads), 0, reinterpret_cast<cudaStream_t>(stream), peers,
-                           c->rank, c->world, (__half*)resid, (const __half*)bias, n_elems, row_len));
+                           static_cast<P2pControl*>(c->local), static_cast<const __half*>(onellm_p2p_send_buffer(h, which)),
+                           (const uint2*)c->recv_slot(c->local, which, 0), c->slot_words(), c->rank, c->world, (__half*)resid,
+                           (const __half*)bias, n_elems, row_len));
     return ONELLM_OK;
 }
 

@@ -227,6 +227,7 @@ extern "C" int onellm_gemm_ld(int dtype, const void* x, const void* W, void* y, 
     if (dtype == ONELLM_F32) {
         const dim3 grid((N + 63) / 64, (M + 63) / 64);
         ONELLM_REQUIRE(grid.y <= 65535, ONELLM_ERR_UNSUPPORTED, "gemm: M too large for the fp32 path");
+        note_launch();
         if (w_layout == ONELLM_W_NK)
             sgemm_kernel<true><<<grid, 256, 0, st>>>((const float*)x, (const float*)W, (float*)y, M, N, K, ldy);
         else

@@ -485,6 +485,7 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
+    note_launch();
     return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, per_block_final, best_nst, fn, ep);
 }
 
