@@ -1,10 +1,14 @@
 """Runs one hot kernel alone on a fixed, small case: the target of `ncu` captures.
 
-    python -m onellm_b200.kernel_cases gate_up|down|qkv|o_proj|lm_head|attn|norm [--iters N] [--batch B] [--ctx C]
+    python -m onellm_b200.kernel_cases gate_up|down|qkv|o_proj|lm_head|attn|norm|prefill_* [--iters N] [--batch B] [--ctx C]
+                                       [--tp T] [--graph]
 
 Each case holds a few hundred MB on the device (more than the 126 MB L2, far less than a
 full model) and launches the kernel `--iters` times on rotating buffers; it prints the mean
-time per launch from CUDA events and the algorithmic GB/s.
+time per launch from CUDA events and the algorithmic GB/s (TFLOP/s for the prefill cases).
+`--tp T` uses the per-rank shapes of T-way tensor parallelism; `--graph` times the launches as
+one CUDA graph, i.e. back to back on the device without the host's launch cost (what a decode
+step sees).
 """
 from __future__ import annotations
 
