@@ -352,6 +352,14 @@ ONELLM_API int onellm_p2p_connect(onellm_p2p* comm, const void* handles /* world
 ONELLM_API void* onellm_p2p_send_buffer(onellm_p2p* comm, int which);
 ONELLM_API int onellm_p2p_allreduce_add(onellm_p2p* comm, int dtype, int which, void* resid, const void* bias,
                                         int n_elems, int row_len, void* stream);
+/* Projection and all-reduce in ONE kernel (F16, 1 <= M <= 64, [K,N] weights):
+ *     resid[M,N] <- resid + bias + sum over ranks of (x[M,K] . W_r),   W_r = this rank's rows of the weight.
+ * The block that has finished two output elements pushes them to every peer at once and gathers the peers'
+ * values of the same elements, so the link latency hides behind the rest of the projection.  Same rules as
+ * above: identical calls on every rank, receive buffers 0 and 1 alternately, bounded waits.  Must not be
+ * mixed with a concurrent onellm_p2p_allreduce_add on the same `which`. */
+ONELLM_API int onellm_p2p_gemm_allreduce_add(onellm_p2p* comm, int dtype, int which, const void* x, const void* W,
+                                             void* resid, const void* bias, int M, int N, int K, void* stream);
 ONELLM_API int onellm_p2p_error(onellm_p2p* comm);
 ONELLM_API void onellm_p2p_destroy(onellm_p2p* comm);
 

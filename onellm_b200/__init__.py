@@ -246,6 +246,10 @@ class P2p:
         _check(lib().onellm_p2p_allreduce_add(self._h, C.c_int(F16), C.c_int(which), _p(resid), _p(bias), C.c_int(n_elems),
                                               C.c_int(row_len), _stream(stream)))
 
+    def gemm_allreduce_add(self, which, x, W, resid, bias, M, N, K, stream=None):
+        _check(lib().onellm_p2p_gemm_allreduce_add(self._h, C.c_int(F16), C.c_int(which), _p(x), _p(W), _p(resid), _p(bias),
+                                                   C.c_int(M), C.c_int(N), C.c_int(K), _stream(stream)))
+
     def error(self) -> int:
         return int(lib().onellm_p2p_error(self._h))
 

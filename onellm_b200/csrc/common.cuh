@@ -222,6 +222,20 @@ __device__ __forceinline__ float warp_max(float v)
     return v;
 }
 
+// Tensor-parallel epilogue of a projection (p2p_allreduce.cu owns the buffers): the block that has
+// finished an output element pushes it, as one 8-byte word {two fp16 values, sequence number}, into this
+// rank's slot on every peer, then waits for the peers' words of the same element in its own memory and
+// adds them in rank order.  world <= 1: not in use.
+constexpr int kTpMaxBlocks = 1024;  // sequence counters available to one launch
+struct TpEpilogue {
+    uint2* push[8];        // this rank's slot in the receive buffer of rank r (entry of the own rank unused)
+    const uint2* mine;     // this rank's receive buffer of this call: [world][slot_words]
+    size_t slot_words;
+    int* counters;         // one sequence counter per thread block of the launch
+    int* error;            // set when a bounded wait gave up
+    int rank, world;
+};
+
 inline size_t dtype_size(int dtype) { return dtype == ONELLM_F16 ? 2 : (dtype == ONELLM_F32 ? 4 : 0); }
 
 }  // namespace onellm

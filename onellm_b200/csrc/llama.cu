@@ -317,21 +317,18 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         }
         head_in = m.res;
     } else if (m.p2p_connected) {
-        // tensor parallel over peer memory: o_proj and down_proj leave their partial sums in the two send
-        // buffers; one small kernel per projection reads every rank's partial over NVLink and adds the
-        // sum (and the bias) into this rank's copy of the residual stream.  No norm kernels, no NCCL.
-        __half* send0 = static_cast<__half*>(onellm_p2p_send_buffer(m.p2p, 0));
-        __half* send1 = static_cast<__half*>(onellm_p2p_send_buffer(m.p2p, 1));
+        // tensor parallel over peer memory: o_proj and down_proj reduce over the ranks in their own epilogue
+        // (every finished pair of elements is pushed to the peers and the peers' values gathered) and add
+        // the sum, and the bias, into this rank's copy of the residual stream.  Five kernels per layer as on
+        // one GPU: no all-reduce kernel, no norm kernels, no NCCL.
         RC(embedding_launch(ONELLM_F16, m.d_ids, m.res, nullptr, m.tok_emb, B, h, c.vocab_size, m.d_bad_id, false, st));
         for (int l = 0; l < c.num_layers; l++) {
             const LayerW& L = m.layers[l];
             RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w_qkv, nullptr, m.qkv, B, m.qkv_cols, h, c.rms_eps, nullptr, nullptr, sp));
             RC(attention(l));
-            RC(onellm_gemm_fused(ONELLM_F16, m.attn, L.wo, nullptr, send0, B, h, m.Hl * D, -1.f, nullptr, nullptr, sp));
-            RC(onellm_p2p_allreduce_add(m.p2p, ONELLM_F16, 0, m.res, L.b_o, B * h, h, sp));
+            RC(onellm_p2p_gemm_allreduce_add(m.p2p, ONELLM_F16, 0, m.attn, L.wo, m.res, L.b_o, B, h, m.Hl * D, sp));
             RC(onellm_gemm_fused(ONELLM_F16, m.res, L.w1, L.w3, m.act, B, m.Il, h, c.rms_eps, nullptr, nullptr, sp));
-            RC(onellm_gemm_fused(ONELLM_F16, m.act, L.w2, nullptr, send1, B, h, m.Il, -1.f, nullptr, nullptr, sp));
-            RC(onellm_p2p_allreduce_add(m.p2p, ONELLM_F16, 1, m.res, nullptr, B * h, h, sp));
+            RC(onellm_p2p_gemm_allreduce_add(m.p2p, ONELLM_F16, 1, m.act, L.w2, m.res, nullptr, B, h, m.Il, sp));
         }
         if (mode & MODE_HEAD) {
             RC(onellm_rmsnorm(ONELLM_F16, m.res, m.out_norm, c.rms_eps, B, h, sp));

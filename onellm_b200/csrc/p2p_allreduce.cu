@@ -38,7 +38,8 @@ constexpr int kP2pVecPerThread = 2;                       // 16-byte vectors per
 constexpr long long kP2pWaitCycles = 2000LL * 1000 * 1000;  // a wait for a peer gives up after about a second of SM clocks
 
 // Layout of the block every rank allocates and exports:
-//   [0]            control: counters[kP2pMaxBlocks] (sequence number per thread block), error
+//   [0]            control: counters[kP2pMaxBlocks] (sequence number per thread block), error, the same
+//                  counters again for the projections that push from their own epilogue
 //   [kCtlBytes]    send buffer 0, send buffer 1 (max_elems halfs each; written by this rank's projections)
 //   [..]           receive buffers [2][world][max_elems / 2] of 8-byte words {half2 data, sequence number},
 //                  slot [which][r] written by rank r
@@ -46,6 +47,7 @@ struct P2pControl {
     int counters[kP2pMaxBlocks];
     int error;
     int pad[63];
+    int gemm_counters[kTpMaxBlocks];  // sequence numbers of the projections that reduce in their own epilogue
 };
 constexpr size_t kCtlBytes = (sizeof(P2pControl) + 255) / 256 * 256;
 
@@ -258,6 +260,43 @@ extern "C" int onellm_p2p_allreduce_add(onellm_p2p* h, int dtype, int which, voi
                            static_cast<P2pControl*>(c->local), static_cast<const __half*>(onellm_p2p_send_buffer(h, which)),
                            (const uint2*)c->recv_slot(c->local, which, 0), c->slot_words(), c->rank, c->world, (__half*)resid,
                            (const __half*)bias, n_elems, row_len));
+    return ONELLM_OK;
+}
+
+namespace onellm {
+// skinny_gemm_staged.cu
+cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K, bool dual,
+                                      cudaStream_t st, const __half* resid, const __half* bias, float rms_eps, const TpEpilogue* tp);
+}
+
+// The projection and the all-reduce in ONE kernel: resid <- resid + bias + sum over ranks of (x . W), W this
+// rank's [K, N] slice.  A block that has finished two output elements pushes them to every peer at once and
+// gathers the peers' values of the same elements, so the link latency overlaps the rest of the projection.
+extern "C" int onellm_p2p_gemm_allreduce_add(onellm_p2p* h, int dtype, int which, const void* x, const void* W, void* resid,
+                                             const void* bias, int M, int N, int K, void* stream)
+{
+    P2pComm* c = reinterpret_cast<P2pComm*>(h);
+    ONELLM_REQUIRE(c && x && W && resid, ONELLM_ERR_ARG, "p2p_gemm_allreduce_add: null pointer");
+    ONELLM_REQUIRE(c->connected, ONELLM_ERR_STATE, "p2p_gemm_allreduce_add: call onellm_p2p_connect first");
+    ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "p2p_gemm_allreduce_add: only F16 is implemented");
+    ONELLM_REQUIRE(which == 0 || which == 1, ONELLM_ERR_ARG, "p2p_gemm_allreduce_add: receive buffer 0 or 1");
+    ONELLM_REQUIRE(M >= 1 && M <= 64 && N > 0 && K > 0 && K % 16 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED,
+                   "p2p_gemm_allreduce_add: 1..64 tokens, K %% 16 == 0, N %% 8 == 0");
+    ONELLM_REQUIRE((size_t)M * N <= c->max_elems, ONELLM_ERR_ARG, "p2p_gemm_allreduce_add: %d x %d elements exceed the %zu the communicator holds",
+                   M, N, c->max_elems);
+    ONELLM_REQUIRE(aligned16(x) && aligned16(W) && aligned16(resid) && (!bias || aligned16(bias)) && x != resid, ONELLM_ERR_ARG,
+                   "p2p_gemm_allreduce_add: pointers must be 16-byte aligned and x must not be the residual");
+    TpEpilogue tp = {};
+    for (int r = 0; r < c->world; r++) tp.push[r] = c->recv_slot(c->mapped[r], which, c->rank);
+    tp.mine = c->recv_slot(c->local, which, 0);
+    tp.slot_words = c->slot_words();
+    P2pControl* ctl = static_cast<P2pControl*>(c->local);
+    tp.counters = ctl->gemm_counters;
+    tp.error = &ctl->error;
+    tp.rank = c->rank;
+    tp.world = c->world;
+    ONELLM_CUDA(skinny_kn_staged_dispatch((const __half*)x, (const __half*)W, nullptr, (__half*)resid, M, N, K, false,
+                                          reinterpret_cast<cudaStream_t>(stream), (const __half*)resid, (const __half*)bias, -1.f, &tp));
     return ONELLM_OK;
 }
 

@@ -136,12 +136,12 @@ sgemm_kernel(const float* __restrict__ x, const float* __restrict__ W, float* __
 // skinny_gemm_staged.cu
 cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
                                       int K, bool dual, cudaStream_t st, const __half* resid, const __half* bias,
-                                      float rms_eps);
+                                      float rms_eps, const TpEpilogue* tp);
 
 static cudaError_t skinny_kn_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
                                       int K, bool dual, cudaStream_t st)
 {
-    return skinny_kn_staged_dispatch(x, W0, W1, y, M, N, K, dual, st, nullptr, nullptr, -1.f);
+    return skinny_kn_staged_dispatch(x, W0, W1, y, M, N, K, dual, st, nullptr, nullptr, -1.f, nullptr);
 }
 
 template <int MB, int UK>
@@ -267,7 +267,7 @@ extern "C" int onellm_gemm_fused(int dtype, const void* x, const void* W, const 
     if (M == 0) return ONELLM_OK;
     ONELLM_CUDA(skinny_kn_staged_dispatch((const __half*)x, (const __half*)W, (const __half*)Wu, (__half*)y, M, N, K, Wu != nullptr,
                                           reinterpret_cast<cudaStream_t>(stream), (const __half*)resid, (const __half*)bias,
-                                          rms_eps));
+                                          rms_eps, nullptr));
     return ONELLM_OK;
 }
 

@@ -83,6 +83,7 @@ struct EpilogueArgs {
     float rms_eps;
     int rms;
     int early_dependents;  // release the next kernel before the main loop (it then shares the SM with this one)
+    TpEpilogue tp;         // tensor parallel: y = resid + bias + sum over ranks of this projection (see common.cuh)
 };
 
 template <int MB, bool DUAL, bool FUSED>
@@ -344,43 +345,101 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
             if (t == 0) red_ss[8 * mb + g] = v;
         }
     }
+    // tensor parallel: this block's sequence number for the call (blocks pair up by index across the ranks)
+    __shared__ uint32_t s_seq;
+    const bool tp = !FUSED && ep.tp.world > 1;
+    if (tp && tid == 0) {
+        int* ctr = ep.tp.counters + blockIdx.y * gridDim.x + blockIdx.x;
+        const int n = *ctr + 1;
+        *ctr = n;
+        s_seq = 0x80000000u | (uint32_t)n;  // the high bit keeps these apart from the numbers of the stand-alone all-reduce
+    }
     cluster.sync();
-    const int per_rank = (MP * kBN + KS - 1) / KS;
+    const uint32_t seq = tp ? s_seq : 0u;
+    // every rank of the cluster finishes an even-sized slice of the tile, two adjacent columns per thread
+    const int per_rank = (((MP * kBN + KS - 1) / KS) + 1) & ~1;
     const int e_begin = rank * per_rank, e_end = min(e_begin + per_rank, MP * kBN);
-    for (int e = e_begin + tid; e < e_end; e += kStThreads) {
+    const long long t_start = clock64();
+    for (int e = e_begin + 2 * tid; e < e_end; e += 2 * kStThreads) {
         const int tok = e / kBN, c = e % kBN;
         // all remote loads are issued before the first is used (a cluster has at most 8 ranks): summing as
         // they are requested would pay one distributed-shared-memory round trip per rank
-        float p0[8], p1[8], ps[8];
+        float2 p0[8], p1[8];
+        float ps[8];
 #pragma unroll
         for (int r = 0; r < 8; r++) {
-            p0[r] = p1[r] = ps[r] = 0.f;
+            p0[r] = p1[r] = make_float2(0.f, 0.f);
+            ps[r] = 0.f;
             if (r < KS) {
                 const float* peer = cluster.map_shared_rank(red, r);
-                p0[r] = peer[tok * kRedLd + c];
-                if (DUAL) p1[r] = peer[(MP + tok) * kRedLd + c];
+                p0[r] = make_float2(peer[tok * kRedLd + c], peer[tok * kRedLd + c + 1]);
+                if (DUAL) p1[r] = make_float2(peer[(MP + tok) * kRedLd + c], peer[(MP + tok) * kRedLd + c + 1]);
                 if (!FUSED && ep.rms) ps[r] = peer[NW * MP * kRedLd + tok];
             }
         }
-        float s0 = 0.f, s1 = 0.f, ss = 0.f;
+        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
+        float ss = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; r++) {  // rank order: the sum does not depend on which block does it
-            s0 += p0[r];
-            s1 += p1[r];
+            s0.x += p0[r].x;
+            s0.y += p0[r].y;
+            s1.x += p1[r].x;
+            s1.y += p1[r].y;
             ss += ps[r];
         }
-        if (tok < M && n0 + c < N) {
+        if (tok < M && n0 + c < N) {  // N is even: the second column is inside too
             if (!FUSED && ep.rms) {
                 const float inv = rsqrtf(ss / (float)K + ep.rms_eps);
-                s0 *= inv;
-                s1 *= inv;
+                s0.x *= inv;
+                s0.y *= inv;
+                s1.x *= inv;
+                s1.y *= inv;
             }
-            float v = DUAL ? (s0 / (1.0f + __expf(-s0))) * s1 : s0;
+            float v0 = DUAL ? (s0.x / (1.0f + __expf(-s0.x))) * s1.x : s0.x;
+            float v1 = DUAL ? (s0.y / (1.0f + __expf(-s0.y))) * s1.y : s0.y;
+            const size_t idx = (size_t)tok * N + n0 + c;
+            if (tp) {
+                // push this rank's value of the two elements to every peer, then gather theirs
+                const __half2 own = __floats2half2_rn(v0, v1);
+                const uint32_t word = *reinterpret_cast<const uint32_t*>(&own);
+#pragma unroll
+                for (int r = 0; r < 8; r++)
+                    if (r < ep.tp.world && r != ep.tp.rank)
+                        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(ep.tp.push[r] + idx / 2), "r"(word), "r"(seq)
+                                     : "memory");
+                v0 = v1 = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; r++)
+                    if (r < ep.tp.world) {
+                        uint32_t w = word;
+                        if (r != ep.tp.rank) {
+                            const uint2* src = ep.tp.mine + (size_t)r * ep.tp.slot_words + idx / 2;
+                            uint32_t got;
+                            for (;;) {
+                                asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(w), "=r"(got) : "l"(src) : "memory");
+                                if (got == seq) break;
+                                if (clock64() - t_start > 2000LL * 1000 * 1000) {  // about a second: give up, say so, go on
+                                    atomicExch(ep.tp.error, 1);
+                                    break;
+                                }
+                            }
+                        }
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+                        v0 += f.x;
+                        v1 += f.y;
+                    }
+            }
             if (!FUSED && ep.resid) {
-                v += __half2float(ep.resid[(size_t)tok * N + n0 + c]);
-                if (ep.bias) v += __half2float(ep.bias[n0 + c]);
+                const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(ep.resid + idx));
+                v0 += rr.x;
+                v1 += rr.y;
+                if (ep.bias) {
+                    const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(ep.bias + n0 + c));
+                    v0 += bb.x;
+                    v1 += bb.y;
+                }
             }
-            y[(size_t)tok * N + n0 + c] = __float2half_rn(v);
+            *reinterpret_cast<__half2*>(y + idx) = __floats2half2_rn(v0, v1);
         }
     }
     cluster.sync();  // peers may still be reading this block's tile
@@ -463,6 +522,9 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
             }
         }
         if (best_inflight < 0) {  // nothing fits in one wave: smallest blocks, shallow ring
+            // (not for the tensor-parallel epilogue: its blocks wait for their peers on other GPUs, which is
+            // only free of deadlock when every block of the launch is resident)
+            if (ep.tp.world > 1) return cudaErrorInvalidConfiguration;
             best_ks = 1;
             best_nst = 3;
         }
@@ -471,6 +533,7 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     const size_t xn_final = FUSED ? (size_t)8 * MB * (per_block_final * kKC + 8) * sizeof(__half) : 0;
     const size_t smem_final = std::max(stage * best_nst, red) + xn_final;
     if (smem_final > smem_cap) return cudaErrorInvalidConfiguration;
+    if (ep.tp.world > 1 && (long)col_blocks * best_ks > kTpMaxBlocks) return cudaErrorInvalidConfiguration;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -492,12 +555,12 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
 // One pass of at most 64 tokens.  Called from skinny_gemm.cu.
 cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
                                       int K, bool dual, cudaStream_t st, const __half* resid, const __half* bias,
-                                      float rms_eps)
+                                      float rms_eps, const TpEpilogue* tp)
 {
     const FusedNormArgs none = {nullptr, nullptr, nullptr, nullptr, 0.f};
     // the next kernel is released as soon as this one's first weight copies are out: its blocks cannot
     // become resident before blocks of this kernel retire (shared memory), but its launch latency is hidden
-    const EpilogueArgs ep = {resid, resid ? bias : nullptr, rms_eps, rms_eps >= 0.f ? 1 : 0, 1};
+    const EpilogueArgs ep = {resid, resid ? bias : nullptr, rms_eps, rms_eps >= 0.f ? 1 : 0, 1, tp ? *tp : TpEpilogue{}};
     if (dual) {
         if (M <= 8) return launch_staged<1, true, false>(x, W0, W1, y, M, N, K, none, ep, st);
         if (M <= 16) return launch_staged<2, true, false>(x, W0, W1, y, M, N, K, none, ep, st);
@@ -537,7 +600,7 @@ extern "C" int onellm_add_residual_rmsnorm_gemm(int dtype, const void* x, const 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const __half *xh = (const __half*)x, *w0 = (const __half*)W, *w1 = (const __half*)Wu;
     __half* yh = (__half*)y;
-    const EpilogueArgs no_ep = {nullptr, nullptr, 0.f, 0, 0};
+    const EpilogueArgs no_ep = {nullptr, nullptr, 0.f, 0, 0, TpEpilogue{}};
     cudaError_t e;
     if (Wu)
         e = M <= 8 ? launch_staged<1, true, true>(xh, w0, w1, yh, M, N, K, fn, no_ep, st)

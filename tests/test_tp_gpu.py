@@ -84,6 +84,26 @@ def _p2p_worker(rank, size, port, q):
             torch.cuda.synchronize()
             ok = ok and torch.equal(resid.cpu(), want)
     torch.cuda.synchronize()
+    # the projection that reduces in its own epilogue: resid += bias + sum_r x_r . W_r, ten calls on alternating buffers
+    K, N = 1024, h
+    xs = [[(torch.randn(rows, K, generator=gen)).half() for _ in range(size)] for _ in range(10)]
+    Ws = [(0.05 * torch.randn(K, N, generator=gen)).half() for _ in range(size)]
+    d_W = Ws[rank].cuda()
+    resid2 = resid0.cuda()
+    want2 = resid0.clone().float()
+    for i, per_rank in enumerate(xs):
+        which = i % 2
+        comm.gemm_allreduce_add(which, per_rank[rank].cuda(), d_W, resid2, d_bias if which == 0 else None, rows, N, K)
+        tot = torch.zeros(rows, N)
+        for r in range(size):
+            tot += (per_rank[r].float() @ Ws[r].float()).half().float()     # every partial crosses the link as fp16
+        want2 = (tot + want2 + (bias.float() if which == 0 else 0.0)).half().float()
+    torch.cuda.synchronize()
+    got2 = resid2.float().cpu()
+    fused_err = float((got2 - want2).abs().max() / want2.abs().max())
+    everyone = [None] * size
+    dist.all_gather_object(everyone, resid2.cpu())
+    ok = ok and fused_err < 2e-3 and all(torch.equal(everyone[0], t) for t in everyone)   # bit-identical on every rank
     first_err = comm.error()
     dist.barrier()
     # a call the last rank never joins: the others give up after about a second and say so
