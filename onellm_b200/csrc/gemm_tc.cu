@@ -20,7 +20,7 @@
 #include <algorithm>
 #include <mutex>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace onellm {
 
@@ -34,77 +34,6 @@ constexpr int kTcBTile = kTcBN * kTcBK * 2;        // 32 KB: [K,N] four boxes of
 constexpr int kTcBChunk = 64 * kTcBK * 2;          // 8 KB: one 64-column chunk of a [K,N] stage
 constexpr int kTcStageBytes = kTcATile + kTcBTile;
 constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + 1024 /* alignment slack */ + 256 /* barriers, TMEM address */;
-constexpr uint32_t kSpinLimit = 1u << 24;  // ~0.3 s of polling
-
-__device__ int g_tc_timeout_flag;  // set when a bounded wait gave up
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// bounded wait; returns false (and raises the flag) when the phase never completes
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
-{
-    for (uint32_t i = 0; i < kSpinLimit; i++) {
-        uint32_t ok;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-    }
-    atomicExch(&g_tc_timeout_flag, 1);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-// shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
-{
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
-           (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
-        "[%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // W_NK = false: W [K,N] (B operand MN-major);  W_NK = true: W [N,K] (B operand K-major).
 // Persistent: grid = min(tiles, SMs) blocks of six warps; block c works on tiles c, c + grid, ... in band
@@ -308,7 +237,7 @@ static EncodeTiledFn encode_tiled()
 }
 
 // 2-D fp16 tensor map: `inner` contiguous elements, `outer` rows of `inner` elements; box {64, box_outer}; 128-byte swizzle
-static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_outer)
+int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint32_t box_outer)
 {
     EncodeTiledFn enc = encode_tiled();
     ONELLM_REQUIRE(enc, ONELLM_ERR_CUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
@@ -374,13 +303,13 @@ int gemm_swiglu_f16_large(const __half* x, const __half* Wg, const __half* Wu, _
     return gemm_tc_launch(x, Wg, Wu, out, M, I, K, 2, st);
 }
 
-// 1 when a tensor-core GEMM block gave up a bounded wait since the last call (and clears the flag).
+int attn_tc_timeout_flag();  // context_attn_tc.cu
+
+// 1 when a tensor-core block (projection or context attention) gave up a bounded wait since the last call.
 int gemm_tc_timeout_flag()
 {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_timeout_flag, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_tc_timeout_flag, &zero, sizeof(int));
-    return v;
+    const int a = tc_flag_read_clear(), b = attn_tc_timeout_flag();
+    return (a < 0 || b < 0) ? -1 : (a | b);
 }
 
 }  // namespace onellm

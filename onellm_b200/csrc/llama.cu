@@ -123,6 +123,22 @@ __global__ void fold_gamma_kernel(__half* __restrict__ w, const __half* __restri
         w[i] = __float2half_rn(__half2float(w[i]) * __half2float(gamma[i / cols]));
 }
 
+// dst [cols, rows] = src [rows, cols]^T, 32 x 32 tiles through shared memory
+__global__ void transpose_half_kernel(__half* __restrict__ dst, const __half* __restrict__ src, int rows, int cols)
+{
+    __shared__ __half tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int r = r0 + i, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[i][threadIdx.x] = src[(size_t)r * cols + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+        const int c = c0 + i, r = r0 + threadIdx.x;
+        if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][i];
+    }
+}
+
 __global__ void fill_half_kernel(__half* w, size_t n, float v)
 {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -167,6 +183,7 @@ struct Llama {
     int top_k = 1, literal_walk = 0;
     float temperature = 1.0f;
     bool weights_ready = false, use_graphs = true;
+    int head_layout = ONELLM_W_NK;  // ONELLM_W_KN once finalize_weights has transposed the LM head
     cudaStream_t stream = nullptr;
     std::map<long, cudaGraphExec_t> graphs;
     ncclComm_t comm = nullptr;
@@ -354,7 +371,7 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         }
     }
     if (mode & MODE_HEAD) {
-        RC(onellm_gemm(ONELLM_F16, head_in, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));
+        RC(onellm_gemm(ONELLM_F16, head_in, m.out_w, m.logits, B, c.vocab_size, h, m.head_layout, sp));
         RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
         RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size,
                               c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
@@ -489,7 +506,7 @@ static int prefill_context(Llama& m, int B, int P, int history)
     // position-by-position path does)
     ONELLM_CUDA(cudaMemcpy2DAsync(m.y, (size_t)h * sizeof(__half), y + (size_t)(P - 1) * h, (size_t)P * h * sizeof(__half),
                                   (size_t)h * sizeof(__half), B, cudaMemcpyDeviceToDevice, st));
-    RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, ONELLM_W_NK, sp));
+    RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, m.head_layout, sp));
     RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
     RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
                           m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
@@ -688,6 +705,23 @@ static int finalize_weights(Llama& m)
         fold_gamma_kernel<<<blocks_for(hd * m.Il), 256, 0, st>>>(L.w3, L.ffn_norm, hd, (size_t)m.Il);
         fill_half_kernel<<<blocks_for(hd), 256, 0, st>>>(L.attn_norm, hd, 1.0f);
         fill_half_kernel<<<blocks_for(hd), 256, 0, st>>>(L.ffn_norm, hd, 1.0f);
+    }
+    // The LM head arrives as output.weight [vocab, hidden]; it is kept as [hidden, vocab], the orientation of every
+    // other projection, so that the decode step streams it with the same staged kernel (5.5 TB/s against the
+    // 3.7 TB/s of the register-fed kernel for [N, K] weights) and the context phase uses the MN-major tile path.
+    m.head_layout = ONELLM_W_NK;
+    if (c.vocab_size % 8 == 0) {  // the [K, N] kernels need 16-byte rows
+        const size_t V = c.vocab_size;
+        __half* tmp = nullptr;
+        ONELLM_CUDA(cudaMalloc(&tmp, V * hd * sizeof(__half)));
+        const dim3 grid((unsigned)((hd + 31) / 32), (unsigned)((V + 31) / 32));
+        transpose_half_kernel<<<grid, dim3(32, 8), 0, st>>>(tmp, m.out_w, (int)V, (int)hd);
+        const cudaError_t e1 = cudaMemcpyAsync(m.out_w, tmp, V * hd * sizeof(__half), cudaMemcpyDeviceToDevice, st);
+        const cudaError_t e2 = cudaStreamSynchronize(st);
+        cudaFree(tmp);
+        ONELLM_CUDA(e1);
+        ONELLM_CUDA(e2);
+        m.head_layout = ONELLM_W_KN;
     }
     ONELLM_CHECK_LAUNCH();
     ONELLM_CUDA(cudaStreamSynchronize(st));

@@ -323,6 +323,11 @@ static void fill_rope(RopeTable& rt, int rot_dim, float base)
     for (int i = 0; i < kMaxPairs; i++) rt.denom[i] = (2 * i < rot_dim) ? powf(base, (float)(2 * i) / (float)rot_dim) : 1.f;
 }
 
+// context_attn_tc.cu
+int context_attn_tc_launch(const __half* q, long q_ld, const __half* k_cache, const __half* v_cache, int S_max, long cache_rows,
+                           const int* cu_seqlens, const int* history, int B, int max_q_len, int H, int Hkv, float scale, __half* out,
+                           cudaStream_t st);
+
 }  // namespace onellm
 
 using namespace onellm;
@@ -370,6 +375,10 @@ extern "C" int onellm_context_attn(int dtype, const void* q, long q_ld, const vo
                    ONELLM_ERR_ARG, "context_attn: pointers and strides must keep rows 16-byte aligned");
     ONELLM_REQUIRE(B <= 65535 && H <= 65535, ONELLM_ERR_UNSUPPORTED, "context_attn: grid too large");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // head size 128 and the cache in its standard [B, Hkv, S, D] order: tcgen05 tiles (context_attn_tc.cu)
+    if (D == 128 && cs_s == D && cs_h % D == 0 && cs_b == (long)Hkv * cs_h && max_q_len >= 32)
+        return context_attn_tc_launch((const __half*)q, q_ld, (const __half*)k_cache, (const __half*)v_cache, (int)(cs_h / D),
+                                      (long)B * Hkv * (cs_h / D), cu_seqlens, history_length, B, max_q_len, H, Hkv, scale, (__half*)out, st);
     const dim3 grid((max_q_len + kCtxQ - 1) / kCtxQ, H, B);
     const float sl = scale * 1.4426950408889634f;
     static bool attr64 = false, attr128 = false;

@@ -70,3 +70,32 @@ def test_context_attn(ob, cuda, orc, B, H, Hkv, D, lens, hist):
                     Hkv * S * D, S * D, D, torch.from_numpy(cu).cuda(), torch.tensor(hist, device="cuda", dtype=torch.int32), B,
                     max(lens), H, Hkv, D, D ** -0.5, out)
     assert rel_err(out.float().cpu().numpy(), ref) < 1e-3
+
+
+@pytest.mark.parametrize("B,H,Hkv,lens,hist", [(2, 4, 2, [100, 257], [0, 30]), (1, 2, 2, [128], [128])])
+def test_context_attn_ignores_whatever_lies_behind_the_sequences(ob, cuda, orc, B, H, Hkv, lens, hist):
+    """Cache rows behind history + length hold NaN and Inf bit patterns (a cache that was never cleared): they
+    must not reach the result, although whole 128-row tiles of the cache are loaded."""
+    torch = cuda
+    D = 128
+    rng = np.random.default_rng(9)
+    T = int(np.sum(lens))
+    S = 512
+    qkv = _r16(rng.standard_normal((T, H + 2 * Hkv, D)))
+    kc, vc = _r16(rng.standard_normal((B, Hkv, S, D))), _r16(rng.standard_normal((B, Hkv, S, D)))
+    ref = orc.context_attn(qkv[:, :H], kc, vc, lens, hist)
+    for b in range(B):
+        end = lens[b] + hist[b]
+        kc[b, :, end:] = np.nan
+        vc[b, :, end:] = np.nan
+        vc[b, :, end::2] = np.inf
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    d_qkv = torch.from_numpy(qkv).cuda().half()
+    out = torch.zeros(T, H, D, device="cuda", dtype=torch.float16)
+    ob.context_attn(ob.F16, d_qkv, (H + 2 * Hkv) * D, torch.from_numpy(kc).cuda().half(), torch.from_numpy(vc).cuda().half(),
+                    Hkv * S * D, S * D, D, torch.from_numpy(cu).cuda(), torch.tensor(hist, device="cuda", dtype=torch.int32), B,
+                    max(lens), H, Hkv, D, D ** -0.5, out)
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert rel_err(got, ref) < 1e-3
+    assert ob.lib().onellm_gemm_timeout_flag() == 0
