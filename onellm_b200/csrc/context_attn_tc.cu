@@ -22,12 +22,14 @@
 namespace onellm {
 
 constexpr int kAtQ = 128, kAtKV = 128, kAtD = 128;
-constexpr int kAtThreads = 160;                     // four softmax warps + one control warp
+constexpr int kAtSoftmaxThreads = 256;              // eight warps: two threads per query row, 64 columns each
+constexpr int kAtThreads = kAtSoftmaxThreads + 32;  // + one control warp (TMA and MMA issue)
 constexpr int kAtTile = kAtQ * kAtD * 2;            // 32 KB: two 64-column chunks of [128 rows x 128 bytes]
 constexpr int kAtChunk = kAtTile / 2;               // 16 KB
-constexpr int kAtSmemBytes = 6 * kAtTile + 1024 /* alignment slack */ + 256 /* barriers, TMEM address */;
+constexpr int kAtSmemBytes = 6 * kAtTile + 1024 /* alignment slack */ + 2048 /* barriers, TMEM address, row exchange */;
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kAtThreads)
 context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_constant__ CUtensorMap map_k,
@@ -41,25 +43,28 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
     unsigned char* sV = smem + 3 * kAtTile;   // two buffers
     unsigned char* sP = smem + 5 * kAtTile;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kAtTile);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
-    const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), v_full0 = smem_u32(bars + 3), s_full = smem_u32(bars + 5),
-                   p_full = smem_u32(bars + 6), o_full = smem_u32(bars + 7);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    float* xch = reinterpret_cast<float*>(smem + 6 * kAtTile + 128);  // [2][128]: the two halves of a row meet here
+    const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), v_full0 = smem_u32(bars + 3), s_full0 = smem_u32(bars + 5),
+                   p_full = smem_u32(bars + 7), o_full = smem_u32(bars + 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, h = blockIdx.y, hk = h / (H / Hkv);
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, kAtQ);
+        mbar_init(q_full, kAtSoftmaxThreads);
         for (int s = 0; s < 2; s++) {
             mbar_init(k_full0 + 8 * s, 1);
             mbar_init(v_full0 + 8 * s, 1);
+            mbar_init(s_full0 + 8 * s, 1);
         }
-        mbar_init(s_full, 1);
-        mbar_init(p_full, kAtQ);
+        mbar_init(p_full, kAtSoftmaxThreads);
         mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+        // columns 0-127 and 128-255: two S accumulators (the MMA of the next tile runs under the softmax of this
+        // one), 256-383: P.V of the current tile
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -77,7 +82,7 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
     const int n_tiles = active ? (kv_end + kAtKV - 1) / kAtKV : 0;
     const int cache_row0 = (b * Hkv + hk) * S_max;
 
-    if (warp == 4 && lane == 0 && active) {
+    if (warp == 8 && lane == 0 && active) {
         // ---- control: TMA loads and MMA issue
         bool ok = true;
         auto load_kv = [&](int j) {
@@ -90,26 +95,32 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                 tma_load_2d(smem_u32(sV + s * kAtTile + c * kAtChunk), &map_v, 64 * c, cache_row0 + j * kAtKV, v_full0 + 8 * s);
             }
         };
-        for (int j = 0; j < min(2, n_tiles); j++) load_kv(j);
         // instruction descriptors: D = f32, A = B = f16, M = 128, N = 128; B K-major for S, MN-major for PV
         const uint32_t idesc_s = (1u << 4) | (0u << 16) | ((uint32_t)(kAtKV >> 3) << 17) | ((uint32_t)(kAtQ >> 4) << 24);
         const uint32_t idesc_o = (1u << 4) | (1u << 16) | ((uint32_t)(kAtD >> 3) << 17) | ((uint32_t)(kAtQ >> 4) << 24);
-        ok = mbar_wait(q_full, 0);
-        for (int j = 0; j < n_tiles && ok; j++) {
+        auto issue_s = [&](int j) {  // S_j = Q . K_j^T into accumulator j & 1
             const int s = j & 1;
-            const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-            ok = mbar_wait(k_full0 + 8 * s, ph);
-            if (!ok) break;
+            if (!mbar_wait(k_full0 + 8 * s, (uint32_t)(j >> 1) & 1u)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK + s * kAtTile);
 #pragma unroll
             for (int kk = 0; kk < kAtD / 16; kk++) {
                 // both K-major: 64-column chunk kk/4, 32 bytes per 16 k inside the 128-byte row, 8-row groups 1024 bytes apart
                 const uint32_t off = (kk >> 2) * kAtChunk + (kk & 3) * 32;
-                umma_f16(tmem_base, umma_desc(q_addr + off, 16, 1024), umma_desc(k_addr + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                umma_f16(tmem_base + (uint32_t)(s * 128), umma_desc(q_addr + off, 16, 1024), umma_desc(k_addr + off, 16, 1024), idesc_s,
+                         kk > 0 ? 1u : 0u);
             }
-            umma_commit(s_full);
-            ok = mbar_wait(p_full, (uint32_t)j & 1u) && mbar_wait(v_full0 + 8 * s, ph);
+            umma_commit(s_full0 + 8 * s);
+            return true;
+        };
+        for (int j = 0; j < min(2, n_tiles); j++) load_kv(j);
+        ok = mbar_wait(q_full, 0) && issue_s(0);
+        for (int j = 0; j < n_tiles && ok; j++) {
+            const int s = j & 1;
+            // the next tile's scores while the softmax warps work on this one (its accumulator was last read for
+            // tile j - 1, whose P has been waited for below in the previous round)
+            if (j + 1 < n_tiles) ok = issue_s(j + 1);
+            ok = ok && mbar_wait(p_full, (uint32_t)j & 1u) && mbar_wait(v_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t p_addr = smem_u32(sP), v_addr = smem_u32(sV + s * kAtTile);
@@ -118,120 +129,125 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                 // A = P, K-major over the cache rows of the tile; B = V_tile, MN-major: 64-column chunks 16 KB apart (LBO),
                 // 8-row groups 1024 bytes apart (SBO), 16 rows = 2048 bytes further
                 const uint32_t aoff = (kk >> 2) * kAtChunk + (kk & 3) * 32;
-                umma_f16(tmem_base + 128u, umma_desc(p_addr + aoff, 16, 1024), umma_desc(v_addr + kk * 2048, kAtChunk, 1024), idesc_o,
+                umma_f16(tmem_base + 256u, umma_desc(p_addr + aoff, 16, 1024), umma_desc(v_addr + kk * 2048, kAtChunk, 1024), idesc_o,
                          kk > 0 ? 1u : 0u);
             }
             umma_commit(o_full);
             ok = mbar_wait(o_full, (uint32_t)j & 1u);  // K and V buffers s, and P, are free again
             if (ok && j + 2 < n_tiles) load_kv(j + 2);
         }
-    } else if (warp < 4 && active) {
-        // ---- softmax and output: thread = query row
-        const int r = warp * 32 + lane;
+    } else if (warp < 8 && active) {
+        // ---- softmax and output: two threads per query row, columns [64 * half, 64 * half + 64) of every tile
+        const int r = (warp & 3) * 32 + lane;       // tensor-memory lane = query row (a warp reaches lanes 32 * (warp % 4) ..)
+        const int half = warp >> 2;
         const int pos = hist + q0 + r;              // last cache row this query attends
         const bool row_ok = r < q_rows;
-        const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * 64);
+        const uint32_t row_off = (r >> 3) * 1024 + (r & 7) * 128;  // this row inside a swizzled [128 x 128-byte] chunk
         float m_run = -INFINITY, l_run = 0.f;
-        float o[kAtD];
+        float o[64];
 #pragma unroll
-        for (int i = 0; i < kAtD; i++) o[i] = 0.f;
+        for (int i = 0; i < 64; i++) o[i] = 0.f;
         bool ok = true;
         {
-            // this thread's query row into the Q tile, in the swizzled K-major form a TMA load would give it (rows
-            // behind the end of the sequence are zero): the packed q buffer has no row count the host could put
+            // this thread's half of its query row into the Q tile, in the swizzled K-major form a TMA load would give it
+            // (rows behind the end of the sequence are zero): the packed q buffer has no row count the host could put
             // into a tensor map without reading cu_seqlens back
-            const __half* qrow = q + (size_t)(tok0 + q0 + r) * q_ld + (size_t)h * kAtD;
+            const __half* qrow = q + (size_t)(tok0 + q0 + r) * q_ld + (size_t)h * kAtD + half * 64;
 #pragma unroll
-            for (int u = 0; u < 16; u++) {
+            for (int u = 0; u < 8; u++) {
                 const uint4 v = row_ok ? *reinterpret_cast<const uint4*>(qrow + u * 8) : make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(sQ + (u >> 3) * kAtChunk + (r >> 3) * 1024 + (r & 7) * 128 + (((u & 7) ^ (r & 7)) << 4)) = v;
+                *reinterpret_cast<uint4*>(sQ + half * kAtChunk + row_off + ((u ^ (r & 7)) << 4)) = v;
             }
             fence_async_smem();
             mbar_arrive(q_full);
         }
         for (int j = 0; j < n_tiles; j++) {
-            ok = mbar_wait(s_full, (uint32_t)j & 1u);
+            // Every thread passes both named barriers of every tile whatever happens: after a wait that ran out
+            // (ok == false) the rest of the work is skipped, never a barrier, so no warp is left waiting for another.
+            ok = ok && mbar_wait(s_full0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int kv0 = j * kAtKV;
-            bool okv = true;
-            const bool need_mask = kv0 + kAtKV - 1 > hist + q0;  // some query of the block cannot see the whole tile
-            // pass 1: row maximum
+            uint32_t sv[64];
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kAtKV; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(t_row + (uint32_t)c, v);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int kv0 = j * kAtKV + half * 64;  // first cache row of this thread's columns
+                const bool need_mask = j * kAtKV + kAtKV - 1 > hist + q0;  // some query of the block cannot see the whole tile
+                tmem_ld32(t_row + (uint32_t)((j & 1) * 128), *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+                tmem_ld32(t_row + (uint32_t)((j & 1) * 128 + 32), *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float sv = __uint_as_float(v[i]) * scale_log2e;
-                    if (!need_mask || kv0 + c + i <= pos) mx = fmaxf(mx, sv);
+                for (int i = 0; i < 64; i++) {
+                    float x = __uint_as_float(sv[i]) * scale_log2e;
+                    if (need_mask && kv0 + i > pos) x = -INFINITY;
+                    sv[i] = __float_as_uint(x);
+                    mx = fmaxf(mx, x);
+                }
+                xch[half * 128 + r] = mx;
+            }
+            softmax_barrier();  // the row maximum over both halves
+            float alpha = 1.f;
+            if (ok) {
+                const float m_new = fmaxf(m_run, fmaxf(mx, xch[(half ^ 1) * 128 + r]));
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with nothing to attend yet
+                alpha = fast_exp2(m_run - m_use);                      // exp2(-inf) = 0 on the first tile
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 64; i++) {
+                    const float pv = fast_exp2(__uint_as_float(sv[i]) - m_use);  // exp2(-inf) = 0 for masked columns
+                    sum += pv;
+                    sv[i] = __float_as_uint(pv);
+                }
+                // P (fp16) into chunk `half` of the P tile: 16-byte unit u of the row, XOR-ed with r % 8
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    *reinterpret_cast<uint4*>(sP + half * kAtChunk + row_off + ((u ^ (r & 7)) << 4)) =
+                        make_uint4(pack_h2(__uint_as_float(sv[8 * u]), __uint_as_float(sv[8 * u + 1])),
+                                   pack_h2(__uint_as_float(sv[8 * u + 2]), __uint_as_float(sv[8 * u + 3])),
+                                   pack_h2(__uint_as_float(sv[8 * u + 4]), __uint_as_float(sv[8 * u + 5])),
+                                   pack_h2(__uint_as_float(sv[8 * u + 6]), __uint_as_float(sv[8 * u + 7])));
+                }
+                l_run = l_run * alpha + sum;  // this thread's half of the row sum; the halves meet at the end
+                m_run = m_new;
+                if (j * kAtKV + kAtKV > kv_end) {
+                    // The tile reaches beyond the rows that exist: what the cache holds there is arbitrary (possibly
+                    // NaN bit patterns), and 0 x NaN would poison the product.  Thread (r, half) clears chunk `half`
+                    // of cache row r of the V tile.
+                    ok = mbar_wait(v_full0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u);
+                    if (ok && j * kAtKV + r >= kv_end) {
+#pragma unroll
+                        for (int u = 0; u < 8; u++)
+                            *reinterpret_cast<uint4*>(sV + (j & 1) * kAtTile + half * kAtChunk + row_off + u * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                if (ok) {
+                    fence_async_smem();  // P (and V rows) went through the generic proxy; the MMA reads through the async proxy
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(p_full);
+                    ok = mbar_wait(o_full, (uint32_t)j & 1u);  // P.V of this tile
                 }
             }
-            const float m_new = fmaxf(m_run, mx);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with nothing to attend yet
-            const float alpha = fast_exp2(m_run - m_use);          // exp2(-inf) = 0 on the first tile
-            // pass 2: exponentials, row sum, P to shared memory (fp16, swizzled K-major)
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < kAtKV; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(t_row + (uint32_t)c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float p[32];
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float sv = __uint_as_float(v[i]) * scale_log2e;
-                    p[i] = (!need_mask || kv0 + c + i <= pos) ? fast_exp2(sv - m_use) : 0.f;
-                    sum += p[i];
-                }
-                // 16-byte unit u = (c + 8q) / 8 of the row; chunk u / 8; unit inside the 128-byte row XOR-ed with r % 8
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int u = (c >> 3) + q;
-                    unsigned char* dst = sP + (u >> 3) * kAtChunk + (r >> 3) * 1024 + (r & 7) * 128 + (((u & 7) ^ (r & 7)) << 4);
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_h2(p[8 * q], p[8 * q + 1]), pack_h2(p[8 * q + 2], p[8 * q + 3]),
-                                                                pack_h2(p[8 * q + 4], p[8 * q + 5]), pack_h2(p[8 * q + 6], p[8 * q + 7]));
-                }
-            }
-            l_run = l_run * alpha + sum;
-            m_run = m_new;
-            if (kv0 + kAtKV > kv_end) {
-                // The tile reaches beyond the rows that exist: what the cache holds there is arbitrary (possibly NaN
-                // bit patterns), and 0 x NaN would poison the product.  Thread r clears cache row r of the V tile.
-                okv = mbar_wait(v_full0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u);
-                if (okv && kv0 + r >= kv_end) {
-                    unsigned char* vrow = sV + (j & 1) * kAtTile + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
-                    for (int c = 0; c < 2; c++)
-#pragma unroll
-                        for (int u = 0; u < 8; u++) *reinterpret_cast<uint4*>(vrow + c * kAtChunk + u * 16) = make_uint4(0u, 0u, 0u, 0u);
-                }
-            }
-            fence_async_smem();  // P (and V rows) were written through the generic proxy; the MMA reads them through the async proxy
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_full);
-            // PV of this tile
-            ok = mbar_wait(o_full, (uint32_t)j & 1u) && okv;
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < kAtD; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(t_row + 128u + (uint32_t)c, v);
+            if (ok) {
+                // output columns [64 * half, 64 * half + 64)
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 256u + (uint32_t)(half * 64), *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+                tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 256u + (uint32_t)(half * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 32; i++) o[c + i] = o[c + i] * alpha + __uint_as_float(v[i]);
+                for (int i = 0; i < 64; i++) o[i] = o[i] * alpha + __uint_as_float(sv[i]);
             }
+            softmax_barrier();  // the exchange slots are free for the next tile
         }
+        // the two halves of the row sum
+        xch[half * 128 + r] = l_run;
+        softmax_barrier();
+        const float l_row = l_run + xch[(half ^ 1) * 128 + r];
         if (ok && row_ok) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            __half* dst = out + (size_t)(tok0 + q0 + r) * H * kAtD + (size_t)h * kAtD;
+            const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+            __half* dst = out + (size_t)(tok0 + q0 + r) * H * kAtD + (size_t)h * kAtD + half * 64;
 #pragma unroll
-            for (int c = 0; c < kAtD; c += 8) {
+            for (int c = 0; c < 64; c += 8) {
                 *reinterpret_cast<uint4*>(dst + c) =
                     make_uint4(pack_h2(o[c] * inv, o[c + 1] * inv), pack_h2(o[c + 2] * inv, o[c + 3] * inv),
                                pack_h2(o[c + 4] * inv, o[c + 5] * inv), pack_h2(o[c + 6] * inv, o[c + 7] * inv));
@@ -241,7 +257,7 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
