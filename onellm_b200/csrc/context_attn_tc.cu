@@ -26,7 +26,7 @@ constexpr int kAtSoftmaxThreads = 256;              // eight warps: two threads 
 constexpr int kAtThreads = kAtSoftmaxThreads + 32;  // + one control warp (TMA and MMA issue)
 constexpr int kAtTile = kAtQ * kAtD * 2;            // 32 KB: two 64-column chunks of [128 rows x 128 bytes]
 constexpr int kAtChunk = kAtTile / 2;               // 16 KB
-constexpr int kAtSmemBytes = 6 * kAtTile + 1024 /* alignment slack */ + 2048 /* barriers, TMEM address, row exchange */;
+constexpr int kAtSmemBytes = 6 * kAtTile + 1024 /* alignment slack */ + 4096 /* barriers, TMEM address, row exchange */;
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
@@ -85,15 +85,19 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
     if (warp == 8 && lane == 0 && active) {
         // ---- control: TMA loads and MMA issue
         bool ok = true;
-        auto load_kv = [&](int j) {
+        auto load_k = [&](int j) {
             const int s = j & 1;
             mbar_expect_tx(k_full0 + 8 * s, kAtTile);
+#pragma unroll
+            for (int c = 0; c < 2; c++)
+                tma_load_2d(smem_u32(sK + s * kAtTile + c * kAtChunk), &map_k, 64 * c, cache_row0 + j * kAtKV, k_full0 + 8 * s);
+        };
+        auto load_v = [&](int j) {
+            const int s = j & 1;
             mbar_expect_tx(v_full0 + 8 * s, kAtTile);
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                tma_load_2d(smem_u32(sK + s * kAtTile + c * kAtChunk), &map_k, 64 * c, cache_row0 + j * kAtKV, k_full0 + 8 * s);
+            for (int c = 0; c < 2; c++)
                 tma_load_2d(smem_u32(sV + s * kAtTile + c * kAtChunk), &map_v, 64 * c, cache_row0 + j * kAtKV, v_full0 + 8 * s);
-            }
         };
         // instruction descriptors: D = f32, A = B = f16, M = 128, N = 128; B K-major for S, MN-major for PV
         const uint32_t idesc_s = (1u << 4) | (0u << 16) | ((uint32_t)(kAtKV >> 3) << 17) | ((uint32_t)(kAtQ >> 4) << 24);
@@ -113,41 +117,49 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             umma_commit(s_full0 + 8 * s);
             return true;
         };
-        for (int j = 0; j < min(2, n_tiles); j++) load_kv(j);
+        for (int j = 0; j < min(2, n_tiles); j++) {
+            load_k(j);
+            load_v(j);
+        }
         ok = mbar_wait(q_full, 0) && issue_s(0);
         for (int j = 0; j < n_tiles && ok; j++) {
             const int s = j & 1;
             // the next tile's scores while the softmax warps work on this one (its accumulator was last read for
-            // tile j - 1, whose P has been waited for below in the previous round)
+            // tile j - 1, whose P has been waited for in the previous round)
             if (j + 1 < n_tiles) ok = issue_s(j + 1);
+            // K buffer s is free once S_j is complete
+            ok = ok && mbar_wait(s_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
+            if (ok && j + 2 < n_tiles) load_k(j + 2);
             ok = ok && mbar_wait(p_full, (uint32_t)j & 1u) && mbar_wait(v_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t p_addr = smem_u32(sP), v_addr = smem_u32(sV + s * kAtTile);
 #pragma unroll
             for (int kk = 0; kk < kAtKV / 16; kk++) {
-                // A = P, K-major over the cache rows of the tile; B = V_tile, MN-major: 64-column chunks 16 KB apart (LBO),
-                // 8-row groups 1024 bytes apart (SBO), 16 rows = 2048 bytes further
+                // O += P . V_tile.  A = P, K-major over the cache rows of the tile; B = V_tile, MN-major: 64-column
+                // chunks 16 KB apart (LBO), 8-row groups 1024 bytes apart (SBO), 16 rows = 2048 bytes further
                 const uint32_t aoff = (kk >> 2) * kAtChunk + (kk & 3) * 32;
                 umma_f16(tmem_base + 256u, umma_desc(p_addr + aoff, 16, 1024), umma_desc(v_addr + kk * 2048, kAtChunk, 1024), idesc_o,
-                         kk > 0 ? 1u : 0u);
+                         (j > 0 || kk > 0) ? 1u : 0u);
             }
             umma_commit(o_full);
-            ok = mbar_wait(o_full, (uint32_t)j & 1u);  // K and V buffers s, and P, are free again
-            if (ok && j + 2 < n_tiles) load_kv(j + 2);
+            if (j + 2 < n_tiles) {
+                ok = mbar_wait(o_full, (uint32_t)j & 1u);  // V buffer s is free again
+                if (ok) load_v(j + 2);
+            }
         }
     } else if (warp < 8 && active) {
-        // ---- softmax and output: two threads per query row, columns [64 * half, 64 * half + 64) of every tile
+        // ---- softmax and output: two threads per query row, columns [64 * half, 64 * half + 64) of every tile.  O stays
+        // in tensor memory and the MMA accumulates into it; it is rescaled only when a row's maximum has grown by more
+        // than 2^8 over the reference the row's exponentials are taken against (P stays below 256, exact in fp16's range).
         const int r = (warp & 3) * 32 + lane;       // tensor-memory lane = query row (a warp reaches lanes 32 * (warp % 4) ..)
         const int half = warp >> 2;
         const int pos = hist + q0 + r;              // last cache row this query attends
         const bool row_ok = r < q_rows;
-        const uint32_t t_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * 64);
+        const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t t_s = t_lane + (uint32_t)(half * 64), t_o = t_lane + 256u + (uint32_t)(half * 64);
         const uint32_t row_off = (r >> 3) * 1024 + (r & 7) * 128;  // this row inside a swizzled [128 x 128-byte] chunk
-        float m_run = -INFINITY, l_run = 0.f;
-        float o[64];
-#pragma unroll
-        for (int i = 0; i < 64; i++) o[i] = 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         {
             // this thread's half of its query row into the Q tile, in the swizzled K-major form a TMA load would give it
@@ -163,18 +175,19 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             mbar_arrive(q_full);
         }
         for (int j = 0; j < n_tiles; j++) {
-            // Every thread passes both named barriers of every tile whatever happens: after a wait that ran out
-            // (ok == false) the rest of the work is skipped, never a barrier, so no warp is left waiting for another.
+            // Every thread passes the named barrier of every tile whatever happens: after a wait that ran out
+            // (ok == false) the rest of the work is skipped, never the barrier, so no warp is left waiting for another.
             ok = ok && mbar_wait(s_full0 + 8 * (j & 1), (uint32_t)(j >> 1) & 1u);
             ok = __all_sync(0xffffffffu, ok);
             uint32_t sv[64];
             float mx = -INFINITY;
+            float* slot = xch + (j & 1) * 256;  // the slots alternate, so one barrier per tile is enough
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int kv0 = j * kAtKV + half * 64;  // first cache row of this thread's columns
                 const bool need_mask = j * kAtKV + kAtKV - 1 > hist + q0;  // some query of the block cannot see the whole tile
-                tmem_ld32(t_row + (uint32_t)((j & 1) * 128), *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-                tmem_ld32(t_row + (uint32_t)((j & 1) * 128 + 32), *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+                tmem_ld32(t_s + (uint32_t)((j & 1) * 128), *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+                tmem_ld32(t_s + (uint32_t)((j & 1) * 128 + 32), *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int i = 0; i < 64; i++) {
@@ -183,21 +196,45 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                     sv[i] = __float_as_uint(x);
                     mx = fmaxf(mx, x);
                 }
-                xch[half * 128 + r] = mx;
+                slot[half * 128 + r] = mx;
             }
             softmax_barrier();  // the row maximum over both halves
-            float alpha = 1.f;
             if (ok) {
-                const float m_new = fmaxf(m_run, fmaxf(mx, xch[(half ^ 1) * 128 + r]));
-                const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with nothing to attend yet
-                alpha = fast_exp2(m_run - m_use);                      // exp2(-inf) = 0 on the first tile
+                const float m_row = fmaxf(mx, slot[(half ^ 1) * 128 + r]);  // the same in both threads of the row
+                const bool grow = m_row > m_ref + 8.f;  // always on the first tile: every row sees cache row 0
+                float alpha = 1.f;
+                if (grow) {
+                    alpha = fast_exp2(m_ref - m_row);  // exp2(-inf) = 0 on the first tile
+                    m_ref = m_row;
+                    l_run *= alpha;
+                }
+                if (j > 0) {
+                    ok = mbar_wait(o_full, (uint32_t)(j - 1) & 1u);  // P.V of the tile before: P is free, O is at rest
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (ok && __any_sync(0xffffffffu, grow)) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        uint32_t ov[32];
+#pragma unroll
+                        for (int c = 0; c < 64; c += 32) {
+                            tmem_ld32(t_o + (uint32_t)c, ov);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                            tmem_st32(t_o + (uint32_t)c, ov);
+                        }
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    }
+                }
+            }
+            if (ok) {
                 float sum = 0.f;
 #pragma unroll
                 for (int i = 0; i < 64; i++) {
-                    const float pv = fast_exp2(__uint_as_float(sv[i]) - m_use);  // exp2(-inf) = 0 for masked columns
+                    const float pv = fast_exp2(__uint_as_float(sv[i]) - m_ref);  // exp2(-inf) = 0 for masked columns
                     sum += pv;
                     sv[i] = __float_as_uint(pv);
                 }
+                l_run += sum;  // this thread's half of the row sum; the halves meet at the end
                 // P (fp16) into chunk `half` of the P tile: 16-byte unit u of the row, XOR-ed with r % 8
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
@@ -207,8 +244,6 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                                    pack_h2(__uint_as_float(sv[8 * u + 4]), __uint_as_float(sv[8 * u + 5])),
                                    pack_h2(__uint_as_float(sv[8 * u + 6]), __uint_as_float(sv[8 * u + 7])));
                 }
-                l_run = l_run * alpha + sum;  // this thread's half of the row sum; the halves meet at the end
-                m_run = m_new;
                 if (j * kAtKV + kAtKV > kv_end) {
                     // The tile reaches beyond the rows that exist: what the cache holds there is arbitrary (possibly
                     // NaN bit patterns), and 0 x NaN would poison the product.  Thread (r, half) clears chunk `half`
@@ -224,33 +259,33 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                     fence_async_smem();  // P (and V rows) went through the generic proxy; the MMA reads through the async proxy
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbar_arrive(p_full);
-                    ok = mbar_wait(o_full, (uint32_t)j & 1u);  // P.V of this tile
                 }
             }
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                // output columns [64 * half, 64 * half + 64)
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 256u + (uint32_t)(half * 64), *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-                tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 256u + (uint32_t)(half * 64 + 32), *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 64; i++) o[i] = o[i] * alpha + __uint_as_float(sv[i]);
-            }
-            softmax_barrier();  // the exchange slots are free for the next tile
         }
-        // the two halves of the row sum
+        // the two halves of the row sum, then O out of tensor memory
+        softmax_barrier();
         xch[half * 128 + r] = l_run;
         softmax_barrier();
         const float l_row = l_run + xch[(half ^ 1) * 128 + r];
-        if (ok && row_ok) {
-            const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-            __half* dst = out + (size_t)(tok0 + q0 + r) * H * kAtD + (size_t)h * kAtD + half * 64;
+        ok = ok && mbar_wait(o_full, (uint32_t)(n_tiles - 1) & 1u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t ov[64];
+            tmem_ld32(t_o, *reinterpret_cast<uint32_t(*)[32]>(&ov[0]));
+            tmem_ld32(t_o + 32u, *reinterpret_cast<uint32_t(*)[32]>(&ov[32]));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row_ok) {
+                const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+                __half* dst = out + (size_t)(tok0 + q0 + r) * H * kAtD + (size_t)h * kAtD + half * 64;
 #pragma unroll
-            for (int c = 0; c < 64; c += 8) {
-                *reinterpret_cast<uint4*>(dst + c) =
-                    make_uint4(pack_h2(o[c] * inv, o[c + 1] * inv), pack_h2(o[c + 2] * inv, o[c + 3] * inv),
-                               pack_h2(o[c + 4] * inv, o[c + 5] * inv), pack_h2(o[c + 6] * inv, o[c + 7] * inv));
+                for (int c = 0; c < 64; c += 8) {
+                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(
+                        pack_h2(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv),
+                        pack_h2(__uint_as_float(ov[c + 2]) * inv, __uint_as_float(ov[c + 3]) * inv),
+                        pack_h2(__uint_as_float(ov[c + 4]) * inv, __uint_as_float(ov[c + 5]) * inv),
+                        pack_h2(__uint_as_float(ov[c + 6]) * inv, __uint_as_float(ov[c + 7]) * inv));
+                }
             }
         }
     }
