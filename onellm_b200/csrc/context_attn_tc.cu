@@ -92,38 +92,56 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
     const int n_tiles = active ? (kv_end + kAtKV - 1) / kAtKV : 0;
     const int cache_row0 = (b * Hkv + hk) * S_max;
 
-    if (warp == 4 && lane == 0 && active) {
-        // ---- control: TMA loads and MMA issue
+    if (warp == 4 && active) {
+        // ---- control: TMA loads and MMA issue.  The whole warp runs this code and one elected lane issues the
+        // single-thread instructions: with warp-uniform control flow the descriptors and addresses stay in uniform
+        // registers, which is where tcgen05.mma takes them from (under a divergent `lane == 0` branch every operand
+        // of every MMA was moved there one by one, ~100 cycles per instruction).
+        uint32_t leader;
+        asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(leader));
         bool ok = true;
         auto load_k = [&](int j) {
             const int s = j & 1;
-            mbar_expect_tx(k_full0 + 8 * s, kAtKVTile);
+            if (leader) {
+                mbar_expect_tx(k_full0 + 8 * s, kAtKVTile);
 #pragma unroll
-            for (int c = 0; c < 2; c++)
-                tma_load_2d(smem_u32(sK + s * kAtKVTile + c * kAtKVChunk), &map_k, 64 * c, cache_row0 + j * kAtKV, k_full0 + 8 * s);
+                for (int c = 0; c < 2; c++)
+                    tma_load_2d(smem_u32(sK + s * kAtKVTile + c * kAtKVChunk), &map_k, 64 * c, cache_row0 + j * kAtKV, k_full0 + 8 * s);
+            }
         };
         auto load_v = [&](int j) {
             const int s = j & 1;
-            mbar_expect_tx(v_full0 + 8 * s, kAtKVTile);
+            if (leader) {
+                mbar_expect_tx(v_full0 + 8 * s, kAtKVTile);
 #pragma unroll
-            for (int c = 0; c < 2; c++)
-                tma_load_2d(smem_u32(sV + s * kAtKVTile + c * kAtKVChunk), &map_v, 64 * c, cache_row0 + j * kAtKV, v_full0 + 8 * s);
+                for (int c = 0; c < 2; c++)
+                    tma_load_2d(smem_u32(sV + s * kAtKVTile + c * kAtKVChunk), &map_v, 64 * c, cache_row0 + j * kAtKV, v_full0 + 8 * s);
+            }
         };
+        auto wait_all = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
         // instruction descriptors: D = f32, A = B = f16, M = 128; S: N = 64, B K-major; O: N = 128, B MN-major
         const uint32_t idesc_s = (1u << 4) | (0u << 16) | ((uint32_t)(kAtKV >> 3) << 17) | ((uint32_t)(kAtQ >> 4) << 24);
         const uint32_t idesc_o = (1u << 4) | (1u << 16) | ((uint32_t)(kAtD >> 3) << 17) | ((uint32_t)(kAtQ >> 4) << 24);
+        // Shared-memory descriptors are built once; a step inside a tile only adds (bytes >> 4) to the address field in
+        // the low word (the field holds any shared-memory address, so the add never carries out of it).
+        const uint64_t dq = umma_desc(smem_u32(sQ), 16, 1024), dk = umma_desc(smem_u32(sK), 16, 1024),
+                       dp = umma_desc(smem_u32(sP), 16, 1024), dv = umma_desc(smem_u32(sV), kAtKVChunk, 1024);
         auto issue_s = [&](int j) {  // S_j = Q . K_j^T into accumulator j & 1
             const int s = j & 1;
-            if (!mbar_wait(k_full0 + 8 * s, (uint32_t)(j >> 1) & 1u)) return false;
+            if (!wait_all(k_full0 + 8 * s, (uint32_t)(j >> 1) & 1u)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK + s * kAtKVTile);
+            const uint64_t dks = dk + (uint64_t)(s * (kAtKVTile >> 4));
+            const uint32_t acc = tmem_base + (uint32_t)(s * kAtKV);
+            if (leader) {
 #pragma unroll
-            for (int kk = 0; kk < kAtD / 16; kk++) {
-                // both K-major: 64-column chunk kk/4, 32 bytes per 16 k inside the 128-byte row, 8-row groups 1024 bytes apart
-                umma_f16(tmem_base + (uint32_t)(s * kAtKV), umma_desc(q_addr + (kk >> 2) * kAtQChunk + (kk & 3) * 32, 16, 1024),
-                         umma_desc(k_addr + (kk >> 2) * kAtKVChunk + (kk & 3) * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < kAtD / 16; kk++) {
+                    // both K-major: 64-column chunk kk/4, 32 bytes per 16 k inside the 128-byte row, 8-row groups 1024 bytes apart
+                    umma_f16(acc, dq + (uint64_t)(((kk >> 2) * kAtQChunk + (kk & 3) * 32) >> 4),
+                             dks + (uint64_t)(((kk >> 2) * kAtKVChunk + (kk & 3) * 32) >> 4), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full0 + 8 * s);
             }
-            umma_commit(s_full0 + 8 * s);
+            __syncwarp();
             return true;
         };
         load_k(0);
@@ -132,30 +150,33 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             load_k(1);
             load_v(1);
         }
-        ok = mbar_wait(q_full, 0) && issue_s(0);
+        ok = wait_all(q_full, 0) && issue_s(0);
         for (int j = 0; j < n_tiles && ok; j++) {
             const int s = j & 1;
             // the next tile's scores while the softmax warps work on this one (its accumulator was last read for
             // tile j - 1, whose P has been waited for in the previous round)
             if (j + 1 < n_tiles) ok = issue_s(j + 1);
             // K buffer s is free once S_j is complete
-            ok = ok && mbar_wait(s_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
+            ok = ok && wait_all(s_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
             if (ok && j + 2 < n_tiles) load_k(j + 2);
-            ok = ok && mbar_wait(p_full, (uint32_t)j & 1u) && mbar_wait(v_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
+            ok = ok && wait_all(p_full, (uint32_t)j & 1u) && wait_all(v_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t p_addr = smem_u32(sP), v_addr = smem_u32(sV + s * kAtKVTile);
+            const uint64_t dvs = dv + (uint64_t)(s * (kAtKVTile >> 4));
+            if (leader) {
 #pragma unroll
-            for (int kk = 0; kk < kAtKV / 16; kk++) {
-                // O += P . V_tile.  A = P, K-major over the 64 cache rows of the tile (one 128-byte row per query); B =
-                // V_tile, MN-major: 64-column chunks 8 KB apart (LBO), 8-row groups 1024 bytes apart (SBO), 16 rows =
-                // 2048 bytes further
-                umma_f16(tmem_base + 128u, umma_desc(p_addr + kk * 32, 16, 1024), umma_desc(v_addr + kk * 2048, kAtKVChunk, 1024), idesc_o,
-                         (j > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kAtKV / 16; kk++) {
+                    // O += P . V_tile.  A = P, K-major over the 64 cache rows of the tile (one 128-byte row per query); B =
+                    // V_tile, MN-major: 64-column chunks 8 KB apart (LBO), 8-row groups 1024 bytes apart (SBO), 16 rows =
+                    // 2048 bytes further
+                    umma_f16(tmem_base + 128u, dp + (uint64_t)((kk * 32) >> 4), dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
+                             (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(o_full);
             }
-            umma_commit(o_full);
+            __syncwarp();
             if (j + 2 < n_tiles) {
-                ok = mbar_wait(o_full, (uint32_t)j & 1u);  // V buffer s is free again
+                ok = wait_all(o_full, (uint32_t)j & 1u);  // V buffer s is free again
                 if (ok) load_v(j + 2);
             }
         }
