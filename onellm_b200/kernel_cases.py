@@ -23,7 +23,7 @@ H_, D_, HID, INTER, VOCAB = 32, 128, 4096, 11008, 32000
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm", "gate_up_fused", "qkv_fused", "norm8", "prefill_qkv", "prefill_down", "prefill_gate", "prefill_lm"])
+    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm", "gate_up_fused", "qkv_fused", "norm8", "prefill_qkv", "prefill_down", "prefill_gate", "prefill_lm", "prefill_attn"])
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2040)
@@ -62,6 +62,20 @@ def main():
         out = torch.empty(B, N, device="cuda", dtype=torch.float16)
         fn = lambda i: ob.add_residual_rmsnorm_gemm(ob.F16, x, r, None, g, 1e-5, r2, w[i], wu[i], out, B, N, HID)
         nbytes = (2 if a.case == "gate_up_fused" else 1) * HID * N * 2 + 3 * B * HID * 2 + B * N * 2
+    elif a.case == "prefill_attn":
+        # context attention of one layer: --batch sequences of --ctx new tokens each (default 2040 -> use e.g. --ctx 512)
+        P, S = a.ctx, 2048
+        T = B * P
+        q = torch.randn(T, 3 * H_ * D_, device="cuda", dtype=torch.float16)
+        kc = [torch.randn(B, H_, S, D_, device="cuda", dtype=torch.float16) for _ in range(2)]
+        vc = [torch.randn(B, H_, S, D_, device="cuda", dtype=torch.float16) for _ in range(2)]
+        rot = 2
+        cu = torch.arange(0, B + 1, device="cuda", dtype=torch.int32) * P
+        hl = torch.zeros(B, device="cuda", dtype=torch.int32)
+        out = torch.empty(T, H_ * D_, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.context_attn(ob.F16, q.data_ptr(), 3 * H_ * D_, kc[i].data_ptr(), vc[i].data_ptr(), H_ * S * D_, S * D_, D_,
+                                       cu.data_ptr(), hl.data_ptr(), B, P, H_, H_, D_, D_ ** -0.5, out.data_ptr())
+        nbytes = int(B * H_ * 4 * D_ * P * (P + 1) / 2)  # causal-useful flops
     elif a.case.startswith("prefill_"):
         T = 4096 if a.batch == 8 else a.batch
         K, N, lay = {"prefill_qkv": (HID, 3 * HID, ob.W_KN), "prefill_down": (INTER, HID, ob.W_KN),
