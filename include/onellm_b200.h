@@ -87,6 +87,23 @@ ONELLM_API int onellm_decode_attn(int dtype, const void* q, const void* k, const
                                   long out_stride_b, void* workspace, size_t workspace_bytes,
                                   void* stream);
 
+/* onellm_decode_attn for a batch whose sequences have different lengths (what padding_offset /
+ * history_length / input_length carry through the reference's context phase,
+ * src/kernels/cal_paddingoffset.cu:9-32, src/kernels/qkv_bias_and_RoPE.cu:138-143, and its decode
+ * kernel then drops: masked_MHA_kernel has one `step` for the whole batch,
+ * src/kernels/decoder_masked_attn.cu:294).  step_offset: DEVICE int [B], values <= 0, may be NULL;
+ * sequence b attends step + step_offset[b] rows, stores its new row at step + step_offset[b] - 1 and
+ * rotates at rope_pos + step_offset[b].  Everything else as onellm_decode_attn; `step` (and
+ * *step_dev) describe the longest sequence. */
+ONELLM_API int onellm_decode_attn_ragged(int dtype, const void* q, const void* k, const void* v,
+                                         long q_stride_b, long k_stride_b, long v_stride_b,
+                                         const void* bias_q, const void* bias_k, const void* bias_v,
+                                         void* k_cache, void* v_cache, long cs_b, long cs_h, long cs_s,
+                                         int B, int H, int Hkv, int D, int step, const int* step_dev,
+                                         const int* step_offset, int rope_pos, int rot_dim,
+                                         float rope_base, float scale, void* out, long out_stride_b,
+                                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * onellm_decode_attn for callers that cannot allocate device memory.
  * No counterpart in the reference (its layers allocate scratch through BaseAllocator).
@@ -417,6 +434,12 @@ ONELLM_API int onellm_llama_set_prefill_by_decode(onellm_llama* m, int enabled);
  * sequence state.  host_first_ids (may be NULL) receives the first generated token per prompt. */
 ONELLM_API int onellm_llama_prefill(onellm_llama* m, const int* host_ids, int batch, int prompt_len,
                                     int* host_first_ids);
+/* Prompts of different lengths (the ragged batch of src/layers/decoder/context_decoder.cpp:36-134:
+ * padding_offset / input_length): host_ids holds the prompts packed one after the other, lens[b]
+ * tokens each.  Decoding then continues with onellm_llama_decode_step as after onellm_llama_prefill;
+ * every sequence keeps its own length and positions.  onellm_llama_get_state reports the longest. */
+ONELLM_API int onellm_llama_prefill_ragged(onellm_llama* m, const int* host_ids, const int* lens, int batch,
+                                           int* host_first_ids);
 /* A further turn of the same `batch` sequences: n_new more tokens each (host ids [batch, n_new]) behind
  * the positions already in the KV cache, through the context-phase kernels with history_length =
  * the current length (the multi-turn case of src/layers/decoder/context_decoder.cpp:36-134).

@@ -90,6 +90,18 @@ def decode_attn(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias
         C.c_long(out_stride_b), _p(workspace), C.c_size_t(workspace_bytes), _stream(stream)))
 
 
+def decode_attn_ragged(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache,
+                       cs_b, cs_h, cs_s, B, H, Hkv, D, step, step_offset, rope_pos, rot_dim, rope_base, scale, out,
+                       out_stride_b, workspace, workspace_bytes, step_dev=None, stream=None):
+    """decode_attn with a device int [B] of per-sequence offsets (<= 0) to `step`."""
+    _check(lib().onellm_decode_attn_ragged(
+        C.c_int(dtype), _p(q), _p(k), _p(v), C.c_long(q_stride_b), C.c_long(k_stride_b), C.c_long(v_stride_b),
+        _p(bias_q), _p(bias_k), _p(bias_v), _p(k_cache), _p(v_cache), C.c_long(cs_b), C.c_long(cs_h),
+        C.c_long(cs_s), C.c_int(B), C.c_int(H), C.c_int(Hkv), C.c_int(D), C.c_int(step), _p(step_dev),
+        _p(step_offset), C.c_int(rope_pos), C.c_int(rot_dim), C.c_float(rope_base), C.c_float(scale), _p(out),
+        C.c_long(out_stride_b), _p(workspace), C.c_size_t(workspace_bytes), _stream(stream)))
+
+
 def decode_attn_static(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache,
                        cs_b, cs_h, cs_s, B, H, Hkv, D, step, rope_pos, rot_dim, rope_base, scale, out, out_stride_b,
                        step_dev=None, stream=None):
@@ -335,6 +347,16 @@ class Llama:
         out = np.zeros(ids.shape[0], np.int32)
         _check(lib().onellm_llama_prefill(self._h, ids.ctypes.data_as(C.c_void_p), C.c_int(ids.shape[0]),
                                           C.c_int(ids.shape[1]), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def prefill_ragged(self, prompts):
+        """prompts: a list of int32 arrays of different lengths; returns the first sampled id per sequence."""
+        import numpy as np
+        lens = np.array([len(p) for p in prompts], np.int32)
+        ids = np.ascontiguousarray(np.concatenate([np.asarray(p, np.int32) for p in prompts]))
+        out = np.zeros(len(prompts), np.int32)
+        _check(lib().onellm_llama_prefill_ragged(self._h, ids.ctypes.data_as(C.c_void_p), lens.ctypes.data_as(C.c_void_p),
+                                                 C.c_int(len(prompts)), out.ctypes.data_as(C.c_void_p)))
         return out
 
     def extend(self, ids):

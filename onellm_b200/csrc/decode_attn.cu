@@ -40,6 +40,7 @@ struct DecodeAttnParams {
     int B, H, Hkv, D;
     int step;
     const int* step_dev;
+    const int* step_offset;  // optional, per sequence: its step is the common step + step_offset[b] (<= 0)
     int rope_delta;  // position = step + rope_delta
     int rot_dim;
     float scale_log2e;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
     const int hk = h0 / qpk;
     const bool writes_cache = (h0 % qpk) == 0;
 
-    const int step = p.step_dev ? *p.step_dev : p.step;
+    const int step = (p.step_dev ? *p.step_dev : p.step) + (p.step_offset ? p.step_offset[b] : 0);
     const float pos = (float)(step + p.rope_delta);
     const int n_cached = step - 1;
     const int n_split = effective_splits(n_cached, p.chunk);
@@ -339,7 +340,7 @@ __global__ void decode_attn_combine_kernel(const DecodeAttnParams p)
     pdl_launch_dependents();
     pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
-    const int step = p.step_dev ? *p.step_dev : p.step;
+    const int step = (p.step_dev ? *p.step_dev : p.step) + (p.step_offset ? p.step_offset[b] : 0);
     const int n_split = effective_splits(step - 1, p.chunk);
     if (n_split == 1) return;  // the attention kernel wrote the output itself
     const long base = ((long)b * p.H + h) * p.n_split;
@@ -397,7 +398,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32) decode_attn_mma_kernel(const D
     const bool writes_cache = (h0 % qpk) == 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 
-    const int step = p.step_dev ? *p.step_dev : p.step;
+    const int step = (p.step_dev ? *p.step_dev : p.step) + (p.step_offset ? p.step_offset[b] : 0);
     const float pos = (float)(step + p.rope_delta);
     const int n_cached = step - 1;
     const int n_split = effective_splits(n_cached, p.chunk);
@@ -820,13 +821,12 @@ extern "C" size_t onellm_decode_attn_workspace_bytes(int B, int H, int D, int ma
     return worst + 256;
 }
 
-extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const void* v, long q_stride_b,
-                                  long k_stride_b, long v_stride_b, const void* bias_q,
-                                  const void* bias_k, const void* bias_v, void* k_cache, void* v_cache,
-                                  long cs_b, long cs_h, long cs_s, int B, int H, int Hkv, int D, int step,
-                                  const int* step_dev, int rope_pos, int rot_dim, float rope_base,
-                                  float scale, void* out, long out_stride_b, void* workspace,
-                                  size_t workspace_bytes, void* stream)
+static int decode_attn_impl(int dtype, const void* q, const void* k, const void* v, long q_stride_b, long k_stride_b,
+                            long v_stride_b, const void* bias_q, const void* bias_k, const void* bias_v, void* k_cache,
+                            void* v_cache, long cs_b, long cs_h, long cs_s, int B, int H, int Hkv, int D, int step,
+                            const int* step_dev, const int* step_offset, int rope_pos, int rot_dim, float rope_base,
+                            float scale, void* out, long out_stride_b, void* workspace, size_t workspace_bytes,
+                            void* stream)
 {
     ONELLM_REQUIRE(q && k && v && k_cache && v_cache && out, ONELLM_ERR_ARG, "decode_attn: null pointer");
     ONELLM_REQUIRE(B > 0 && H > 0 && Hkv > 0 && D > 0 && step > 0, ONELLM_ERR_ARG,
@@ -858,6 +858,7 @@ extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const
     p.B = B; p.H = H; p.Hkv = Hkv; p.D = D;
     p.step = step;
     p.step_dev = step_dev;
+    p.step_offset = step_offset;
     p.rope_delta = rope_pos - step;
     p.rot_dim = rot_dim < D ? rot_dim : D;
     p.scale_log2e = scale * 1.4426950408889634f;
@@ -913,6 +914,34 @@ extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const
     }
     ONELLM_CHECK_LAUNCH();
     return ONELLM_OK;
+}
+
+extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const void* v, long q_stride_b,
+                                  long k_stride_b, long v_stride_b, const void* bias_q,
+                                  const void* bias_k, const void* bias_v, void* k_cache, void* v_cache,
+                                  long cs_b, long cs_h, long cs_s, int B, int H, int Hkv, int D, int step,
+                                  const int* step_dev, int rope_pos, int rot_dim, float rope_base,
+                                  float scale, void* out, long out_stride_b, void* workspace,
+                                  size_t workspace_bytes, void* stream)
+{
+    return decode_attn_impl(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache, cs_b,
+                            cs_h, cs_s, B, H, Hkv, D, step, step_dev, nullptr, rope_pos, rot_dim, rope_base, scale, out,
+                            out_stride_b, workspace, workspace_bytes, stream);
+}
+
+// Sequences of different lengths in one batch: sequence b attends step + step_offset[b] rows (the new one included),
+// its new row goes to cache row step + step_offset[b] - 1 and its position moves with it.
+extern "C" int onellm_decode_attn_ragged(int dtype, const void* q, const void* k, const void* v, long q_stride_b,
+                                         long k_stride_b, long v_stride_b, const void* bias_q, const void* bias_k,
+                                         const void* bias_v, void* k_cache, void* v_cache, long cs_b, long cs_h,
+                                         long cs_s, int B, int H, int Hkv, int D, int step, const int* step_dev,
+                                         const int* step_offset, int rope_pos, int rot_dim, float rope_base,
+                                         float scale, void* out, long out_stride_b, void* workspace,
+                                         size_t workspace_bytes, void* stream)
+{
+    return decode_attn_impl(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache, cs_b,
+                            cs_h, cs_s, B, H, Hkv, D, step, step_dev, step_offset, rope_pos, rot_dim, rope_base, scale, out,
+                            out_stride_b, workspace, workspace_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

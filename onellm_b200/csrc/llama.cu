@@ -170,6 +170,9 @@ struct Llama {
     // activations
     int *d_ids = nullptr, *d_prompt = nullptr, *d_step = nullptr, *d_out_ids = nullptr, *d_seqlen = nullptr,
         *d_topk_id = nullptr, *d_bad_id = nullptr;
+    // per sequence: cached length minus cur_len (<= 0; all zero unless the prompts had different lengths)
+    int* d_step_off = nullptr;
+    std::vector<int> seq_off;  // host copy
     unsigned char* d_finished = nullptr;
     float *d_topk_val = nullptr, *d_u = nullptr;
     __half *res = nullptr, *y = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr,
@@ -238,6 +241,7 @@ static void carve(Llama& m, Carver& cv)
     m.prompt_cap = c.max_seq_len;
     m.d_prompt = cv.take<int>(B * (size_t)c.max_seq_len);
     m.d_step = cv.take<int>(4);
+    m.d_step_off = cv.take<int>(B);
     m.d_out_ids = cv.take<int>(B);
     m.d_seqlen = cv.take<int>(B);
     m.d_topk_id = cv.take<int>(B * 64);
@@ -310,10 +314,11 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         const __half* bq = L.b_qkv;
         const __half* bk = L.b_qkv ? L.b_qkv + (size_t)m.Hl * D : nullptr;
         const __half* bv = L.b_qkv ? L.b_qkv + (size_t)(m.Hl + m.Hkvl) * D : nullptr;
-        return onellm_decode_attn(ONELLM_F16, q, k, v, m.qkv_cols, m.qkv_cols, m.qkv_cols, bq, bk, bv,
-                                  m.k_cache + (size_t)l * m.cache_layer_elems, m.v_cache + (size_t)l * m.cache_layer_elems,
-                                  cs_b, cs_h, cs_s, B, m.Hl, m.Hkvl, D, step_bound, m.d_step, step_bound - 1, c.rot_dim,
-                                  c.rope_base, scale, m.attn, (long)m.Hl * D, m.attn_ws, m.attn_ws_bytes, sp);
+        return onellm_decode_attn_ragged(ONELLM_F16, q, k, v, m.qkv_cols, m.qkv_cols, m.qkv_cols, bq, bk, bv,
+                                         m.k_cache + (size_t)l * m.cache_layer_elems, m.v_cache + (size_t)l * m.cache_layer_elems,
+                                         cs_b, cs_h, cs_s, B, m.Hl, m.Hkvl, D, step_bound, m.d_step, m.d_step_off,
+                                         step_bound - 1, c.rot_dim, c.rope_base, scale, m.attn, (long)m.Hl * D, m.attn_ws,
+                                         m.attn_ws_bytes, sp);
     };
     const __half* head_in = m.y;
     if (c.tp_size == 1) {
@@ -440,16 +445,31 @@ static int run_step(Llama& m, int mode, int prompt_len)
     return ONELLM_OK;
 }
 
+// row cu[b + 1] - 1 of the packed [T, h] activations -> row b of dst
+__global__ void gather_last_rows_kernel(const __half* __restrict__ src, const int* __restrict__ cu, __half* __restrict__ dst, int h)
+{
+    const __half* s = src + (size_t)(cu[blockIdx.x + 1] - 1) * h;
+    __half* d = dst + (size_t)blockIdx.x * h;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) d[i] = s[i];
+}
+
 // ---- context phase ------------------------------------------------------------------------------
 // All prompt tokens of the batch at once: tensor-core projections (M = batch * prompt_len), the
 // fused QKV bias + RoPE + cache write, causal attention over the cache, then the LM head on the
 // last token of every sequence.  Same arithmetic as running the positions one by one through the
 // decode kernels (which `prefill_by_decode` still does, for cross-checking).
-static int prefill_context(Llama& m, int B, int P, int history)
+// lens[b] new tokens of sequence b (packed in d_prompt in sequence order) behind the cur_len + seq_off[b] positions it
+// has cached.
+static int prefill_context(Llama& m, int B, const int* lens)
 {
     const auto& c = m.c;
     const int h = c.hidden, D = c.head_size;
-    const size_t T = (size_t)B * P;
+    size_t T = 0;
+    int P = 0;
+    for (int b = 0; b < B; b++) {
+        T += (size_t)lens[b];
+        P = lens[b] > P ? lens[b] : P;
+    }
     cudaStream_t st = m.stream;
     void* sp = (void*)st;
     // scratch layout for T tokens
@@ -472,14 +492,22 @@ static int prefill_context(Llama& m, int B, int P, int history)
     __half* act = cv.take<__half>(T * (size_t)m.Il);
     int* d_cu = cv.take<int>(c.max_batch + 1);
     int* d_hist = cv.take<int>(c.max_batch);
-    std::vector<int> cu(B + 1), hist(B, history);
-    for (int b = 0; b <= B; b++) cu[b] = b * P;
+    std::vector<int> cu(B + 1, 0), hist(B), off(B);
+    m.seq_off.resize(c.max_batch, 0);
+    for (int b = 0; b < B; b++) hist[b] = m.cur_len + m.seq_off[b];
+    int new_max = 0;
+    for (int b = 0; b < B; b++) {
+        cu[b + 1] = cu[b] + lens[b];
+        new_max = hist[b] + lens[b] > new_max ? hist[b] + lens[b] : new_max;
+    }
+    for (int b = 0; b < B; b++) off[b] = hist[b] + lens[b] - new_max;
+    ONELLM_CUDA(cudaMemcpyAsync(m.d_step_off, off.data(), B * sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemcpyAsync(d_cu, cu.data(), (B + 1) * sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemcpyAsync(d_hist, hist.data(), B * sizeof(int), cudaMemcpyHostToDevice, st));
-    ONELLM_CUDA(cudaStreamSynchronize(st));  // cu / hist live on this stack frame
+    ONELLM_CUDA(cudaStreamSynchronize(st));  // cu / hist / off live on this stack frame
 
     const long launches_before = launches_noted();
-    // d_prompt is [B, P] row-major = the packed token order
+    // d_prompt holds the new tokens packed in sequence order
     RC(embedding_launch(ONELLM_F16, m.d_prompt, y, res, m.tok_emb, (int)T, h, c.vocab_size, m.d_bad_id, false, st));
     RC(onellm_rmsnorm(ONELLM_F16, y, m.layers[0].attn_norm, c.rms_eps, (int)T, h, sp));
     const long cs_b = (long)m.Hkvl * c.max_seq_len * D, cs_h = (long)c.max_seq_len * D, cs_s = D;
@@ -502,16 +530,17 @@ static int prefill_context(Llama& m, int B, int P, int history)
         const __half* next_gamma = (l + 1 < c.num_layers) ? m.layers[l + 1].attn_norm : m.out_norm;
         RC(onellm_add_residual_rmsnorm(ONELLM_F16, res, y, nullptr, next_gamma, c.rms_eps, (int)T, h, sp));
     }
-    // last position of every sequence -> LM head, top-K, sampling (seeded with step = P, as the
+    // last position of every sequence -> LM head, top-K, sampling (seeded with the step counter, as the
     // position-by-position path does)
-    ONELLM_CUDA(cudaMemcpy2DAsync(m.y, (size_t)h * sizeof(__half), y + (size_t)(P - 1) * h, (size_t)P * h * sizeof(__half),
-                                  (size_t)h * sizeof(__half), B, cudaMemcpyDeviceToDevice, st));
+    note_launch();
+    gather_last_rows_kernel<<<B, 256, 0, st>>>(y, d_cu, m.y, h);
     RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, m.head_layout, sp));
     RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
     RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
                           m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
     m.launches += launches_noted() - launches_before;
-    m.cur_len = history + P;
+    for (int b = 0; b < B; b++) m.seq_off[b] = off[b];
+    m.cur_len = new_max;
     return ONELLM_OK;
 }
 
@@ -879,6 +908,8 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
     m->batch = batch;
     m->graph_prompt_len = prompt_len;
     m->cur_len = 0;
+    m->seq_off.assign(m->c.max_batch, 0);
+    ONELLM_CUDA(cudaMemsetAsync(m->d_step_off, 0, (size_t)m->c.max_batch * sizeof(int), st));
     const int first_step = m->prefill_by_decode ? 0 : prompt_len;  // the step kernels increment before use
     ONELLM_CUDA(cudaMemcpyAsync(m->d_prompt, host_ids, (size_t)batch * prompt_len * sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &first_step, sizeof(int), cudaMemcpyHostToDevice, st));
@@ -891,7 +922,8 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
         for (int p = 0; p < prompt_len; p++)
             RC(run_step(*m, MODE_GATHER | (p == prompt_len - 1 ? MODE_HEAD : 0), prompt_len));
     } else {
-        RC(prefill_context(*m, batch, prompt_len, 0));
+        const std::vector<int> lens(batch, prompt_len);
+        RC(prefill_context(*m, batch, lens.data()));
     }
     if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
     ONELLM_CUDA(cudaStreamSynchronize(st));
@@ -900,6 +932,46 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
     ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_prefill: token id outside [0, vocab_size)");
     ONELLM_REQUIRE(bad[1] == 0, ONELLM_ERR_STATE, "llama_prefill: a position beyond max_seq_len was refused by the cache");
     ONELLM_REQUIRE(onellm_gemm_timeout_flag() <= 0, ONELLM_ERR_CUDA, "llama_prefill: a tensor-core GEMM block timed out");
+    return ONELLM_OK;
+}
+
+// Prompts of different lengths: host_ids holds them packed one after the other, lens[b] tokens each.  Sequence b is
+// cached in rows 0 .. lens[b]-1 of its cache; the step counter follows the longest sequence and the decode attention
+// gives every other sequence its own, shorter, row count and position.
+extern "C" int onellm_llama_prefill_ragged(onellm_llama* h, const int* host_ids, const int* lens, int batch, int* host_first_ids)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m && host_ids && lens, ONELLM_ERR_ARG, "llama_prefill_ragged: null pointer");
+    ONELLM_REQUIRE(m->weights_ready, ONELLM_ERR_STATE, "llama_prefill_ragged: weights not loaded");
+    ONELLM_REQUIRE(batch >= 1 && batch <= m->c.max_batch, ONELLM_ERR_ARG, "llama_prefill_ragged: batch %d outside [1,%d]", batch, m->c.max_batch);
+    size_t total = 0;
+    int longest = 0;
+    for (int b = 0; b < batch; b++) {
+        ONELLM_REQUIRE(lens[b] >= 1 && lens[b] <= m->c.max_seq_len, ONELLM_ERR_ARG, "llama_prefill_ragged: lens[%d] = %d outside [1,%d]", b,
+                       lens[b], m->c.max_seq_len);
+        total += (size_t)lens[b];
+        longest = lens[b] > longest ? lens[b] : longest;
+    }
+    cudaStream_t st = m->stream;
+    ONELLM_CUDA(cudaStreamSynchronize(st));
+    if (batch != m->batch) drop_graphs(*m);
+    m->batch = batch;
+    m->cur_len = 0;
+    m->seq_off.assign(m->c.max_batch, 0);
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_prompt, host_ids, total * sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &longest, sizeof(int), cudaMemcpyHostToDevice, st));
+    ONELLM_CUDA(cudaMemsetAsync(m->d_seqlen, 0, (size_t)batch * sizeof(int), st));
+    ONELLM_CUDA(cudaMemsetAsync(m->d_finished, 0, (size_t)batch, st));
+    ONELLM_CUDA(cudaMemsetAsync(m->d_bad_id, 0, 4 * sizeof(int), st));
+    ONELLM_CUDA(cudaStreamSynchronize(st));  // `longest` lives on this stack frame
+    RC(prefill_context(*m, batch, lens));
+    if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
+    ONELLM_CUDA(cudaStreamSynchronize(st));
+    int bad[2] = {0, 0};
+    ONELLM_CUDA(cudaMemcpy(bad, m->d_bad_id, 2 * sizeof(int), cudaMemcpyDeviceToHost));
+    ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_prefill_ragged: token id outside [0, vocab_size)");
+    ONELLM_REQUIRE(bad[1] == 0, ONELLM_ERR_STATE, "llama_prefill_ragged: a position beyond max_seq_len was refused by the cache");
+    ONELLM_REQUIRE(onellm_gemm_timeout_flag() <= 0, ONELLM_ERR_CUDA, "llama_prefill_ragged: a tensor-core GEMM block timed out");
     return ONELLM_OK;
 }
 
@@ -917,7 +989,8 @@ extern "C" int onellm_llama_extend(onellm_llama* h, const int* host_ids, int n_n
     ONELLM_CUDA(cudaMemcpyAsync(m->d_prompt, host_ids, (size_t)batch * n_new * sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &new_len, sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaStreamSynchronize(st));  // `new_len` lives on this stack frame
-    RC(prefill_context(*m, batch, n_new, m->cur_len));
+    const std::vector<int> lens(batch, n_new);
+    RC(prefill_context(*m, batch, lens.data()));
     if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
     ONELLM_CUDA(cudaStreamSynchronize(st));
     int bad[2] = {0, 0};
@@ -943,6 +1016,8 @@ extern "C" int onellm_llama_seek(onellm_llama* h, int batch, int cur_len, const 
     if (batch != m->batch) drop_graphs(*m);
     m->batch = batch;
     m->cur_len = cur_len;
+    m->seq_off.assign(m->c.max_batch, 0);
+    ONELLM_CUDA(cudaMemsetAsync(m->d_step_off, 0, (size_t)m->c.max_batch * sizeof(int), st));
     ONELLM_CUDA(cudaMemcpyAsync(m->d_step, &cur_len, sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemcpyAsync(m->d_ids, host_ids, (size_t)batch * sizeof(int), cudaMemcpyHostToDevice, st));
     ONELLM_CUDA(cudaMemsetAsync(m->d_seqlen, 0, (size_t)batch * sizeof(int), st));

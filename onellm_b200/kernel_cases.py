@@ -1,6 +1,6 @@
 """Runs one hot kernel alone on a fixed, small case: the target of `ncu` captures.
 
-    python -m onellm_b200.kernel_cases gate_up|down|qkv|o_proj|lm_head|attn|norm|prefill_* [--iters N] [--batch B] [--ctx C]
+    python -m onellm_b200.kernel_cases gate_up|down|qkv|o_proj|lm_head|lm_head_kn|attn|norm|prefill_* [--iters N] [--batch B] [--ctx C]
                                        [--tp T] [--graph]
 
 Each case holds a few hundred MB on the device (more than the 126 MB L2, far less than a
@@ -23,7 +23,7 @@ H_, D_, HID, INTER, VOCAB = 32, 128, 4096, 11008, 32000
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "attn", "norm", "gate_up_fused", "qkv_fused", "norm8", "prefill_qkv", "prefill_down", "prefill_gate", "prefill_lm", "prefill_attn"])
+    ap.add_argument("case", choices=["gate_up", "down", "qkv", "o_proj", "lm_head", "lm_head_kn", "attn", "norm", "gate_up_fused", "qkv_fused", "norm8", "prefill_qkv", "prefill_down", "prefill_gate", "prefill_lm", "prefill_attn"])
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2040)
@@ -97,6 +97,13 @@ def main():
         rot = 2
         out = torch.empty(B, VOCAB, device="cuda", dtype=torch.float16)
         fn = lambda i: ob.gemm(ob.F16, x, w[i], out, B, VOCAB, HID, ob.W_NK)
+        nbytes = VOCAB * HID * 2 + B * HID * 2 + B * VOCAB * 2
+    elif a.case == "lm_head_kn":
+        # the layout the model keeps its LM head in: [hidden, vocab], streamed by the staged kernel
+        x, w = torch.randn(B, HID, device="cuda").half(), [rnd(HID, VOCAB) for _ in range(2)]
+        rot = 2
+        out = torch.empty(B, VOCAB, device="cuda", dtype=torch.float16)
+        fn = lambda i: ob.gemm(ob.F16, x, w[i], out, B, VOCAB, HID, ob.W_KN)
         nbytes = VOCAB * HID * 2 + B * HID * 2 + B * VOCAB * 2
     elif a.case == "attn":
         S = a.ctx + 8

@@ -117,6 +117,44 @@ def test_decode_attn_step_from_device_and_determinism(ob, cuda, orc):
     assert rel_err(c[0], a[0]) < TOL["f16"]
 
 
+@pytest.mark.parametrize("dt,H,Hkv,D,steps,S", [("f16", 8, 8, 128, (333, 100, 17, 1), 512), ("f16", 8, 2, 64, (700, 699, 3), 1024),
+                                               ("f32", 4, 4, 128, (60, 255, 2), 256)])
+def test_decode_attn_ragged_batch(ob, cuda, orc, dt, H, Hkv, D, steps, S):
+    """Every sequence of the batch has its own row count and position (step + step_offset[b]); each must equal the
+    oracle run on that sequence alone.  The step itself comes from device memory, as in a captured decode step."""
+    torch = cuda
+    B = len(steps)
+    rng = np.random.default_rng(12)
+    u = lambda *s: _round(rng.uniform(-1, 1, s), dt)
+    qkv, kc, vc = u(B, H + 2 * Hkv, D), u(B, Hkv, S, D), u(B, Hkv, S, D)
+    bq, bk, bv = u(H * D), u(Hkv * D), u(Hkv * D)
+    for b, st in enumerate(steps):
+        kc[b, :, st - 1:], vc[b, :, st - 1:] = 0, 0
+    refs, kc_ref, vc_ref = [], kc.copy(), vc.copy()
+    for b, st in enumerate(steps):
+        kb, vb = np.ascontiguousarray(kc_ref[b:b + 1]), np.ascontiguousarray(vc_ref[b:b + 1])
+        refs.append(orc.decode_attn(qkv[b:b + 1, :H], qkv[b:b + 1, H:H + Hkv], qkv[b:b + 1, H + Hkv:], kb, vb, st, rope_pos=st - 1,
+                                    bias_q=bq, bias_k=bk, bias_v=bv))
+        kc_ref[b], vc_ref[b] = kb[0], vb[0]
+    ref = np.concatenate(refs)
+    longest = max(steps)
+    d_qkv, d_kc, d_vc = _dev(torch, qkv, dt), _dev(torch, kc, dt), _dev(torch, vc, dt)
+    d_b = [_dev(torch, x, dt) for x in (bq, bk, bv)]
+    off = torch.tensor([st - longest for st in steps], device="cuda", dtype=torch.int32)
+    step_dev = torch.tensor([longest], device="cuda", dtype=torch.int32)
+    out = torch.zeros(B, H, D, device="cuda", dtype=_dt(torch, dt))
+    wsb = ob.decode_attn_workspace_bytes(B, H, D, S)
+    ws = torch.empty(wsb, device="cuda", dtype=torch.uint8)
+    esz, base, ld = d_qkv.element_size(), d_qkv.data_ptr(), (H + 2 * Hkv) * D
+    ob.decode_attn_ragged(ob.F16 if dt == "f16" else ob.F32, base, base + H * D * esz, base + (H + Hkv) * D * esz, ld, ld, ld,
+                          d_b[0], d_b[1], d_b[2], d_kc, d_vc, Hkv * S * D, S * D, D, B, H, Hkv, D, S, off, S - 1, D, 10000.0,
+                          1.0 / np.sqrt(D), out, H * D, ws, wsb, step_dev=step_dev)
+    torch.cuda.synchronize()
+    assert rel_err(out.float().cpu().numpy(), ref) < TOL[dt]
+    assert rel_err(d_kc.float().cpu().numpy(), kc_ref) < TOL[dt]
+    assert rel_err(d_vc.float().cpu().numpy(), vc_ref) < TOL[dt]
+
+
 def test_decode_attn_partial_rotary(ob, cuda, orc):
     got, ref, *_ = _run_decode_attn(ob, cuda, orc, "f32", 2, 4, 4, 128, 40, 64, "bhsd", 5, rot_dim=64)
     assert rel_err(got, ref) < TOL["f32"]

@@ -141,3 +141,69 @@ def test_context_phase_matches_position_by_position(ob, cuda, tmp_path):
     assert rel_err(lb, la) < 3e-3
     assert (a == b).mean() > 0.8
     m.close()
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+def test_ragged_prompts_match_the_oracle_sequence_by_sequence(ob, cuda, orc, tmp_path, graphs):
+    """Prompts of 37, 5 and 64 tokens in one batch (packed context phase with cu_seqlens, then decode steps in which
+    every sequence has its own length and position) against the oracle run on every sequence alone."""
+    from oracle.llama_ref import LlamaRef
+    cfg = dict(CFG, max_seq_len=128)
+    m, w = _make(ob, tmp_path, cfg, seed=21)
+    m.set_graphs(graphs)
+    rng = np.random.default_rng(8)
+    lens = [37, 5, 64]
+    prompts = [rng.integers(0, cfg["vocab_size"], n).astype(np.int32) for n in lens]
+    refs = [LlamaRef(cfg, w, 1) for _ in lens]
+    ref_logits = np.concatenate([r.prefill(p[None, :]) for r, p in zip(refs, prompts)])
+    first = m.prefill_ragged(prompts)
+    got = m.logits(3)
+    assert rel_err(got, ref_logits) < 3e-3
+    assert np.array_equal(first, orc.topk(got, 1)[1][:, 0])
+    ids, out = first.copy(), np.zeros(3, np.int32)
+    for _ in range(5):
+        ref_logits = np.concatenate([r.step(ids[b:b + 1]) for b, r in enumerate(refs)])
+        m.decode_step(None, out)
+        got = m.logits(3)
+        assert rel_err(got, ref_logits) < 3e-3
+        assert np.array_equal(out, orc.topk(got, 1)[1][:, 0])
+        ids = out.copy()
+    assert m.state()[0] == max(lens) + 5
+    m.close()
+
+
+def test_ragged_turn_after_ragged_prompts(ob, cuda, orc, tmp_path):
+    """extend() behind histories of different lengths: context kernels with per-sequence history_length."""
+    from oracle.llama_ref import LlamaRef
+    cfg = dict(CFG, max_seq_len=128)
+    m, w = _make(ob, tmp_path, cfg, seed=22)
+    rng = np.random.default_rng(9)
+    lens = [20, 33, 3]
+    prompts = [rng.integers(0, cfg["vocab_size"], n).astype(np.int32) for n in lens]
+    more = rng.integers(0, cfg["vocab_size"], (3, 9)).astype(np.int32)
+    refs = [LlamaRef(cfg, w, 1) for _ in lens]
+    for r, p in zip(refs, prompts):
+        r.prefill(p[None, :])
+    ref_logits = np.concatenate([r.prefill(more[b:b + 1]) for b, r in enumerate(refs)])
+    m.prefill_ragged(prompts)
+    first = m.extend(more)
+    got = m.logits(3)
+    assert rel_err(got, ref_logits) < 3e-3
+    assert np.array_equal(first, orc.topk(got, 1)[1][:, 0])
+    out = np.zeros(3, np.int32)
+    ref_logits = np.concatenate([r.step(first[b:b + 1]) for b, r in enumerate(refs)])
+    m.decode_step(None, out)
+    assert rel_err(m.logits(3), ref_logits) < 3e-3
+    assert m.state()[0] == 33 + 9 + 1
+    # equal-length prompts afterwards: the per-sequence offsets are back to zero
+    eq = rng.integers(0, cfg["vocab_size"], (3, 11)).astype(np.int32)
+    ref = LlamaRef(cfg, w, 3)
+    ref_logits = ref.prefill(eq)
+    m.prefill(eq)
+    assert rel_err(m.logits(3), ref_logits) < 3e-3
+    ref_logits = ref.step(orc.topk(m.logits(3), 1)[1][:, 0].astype(np.int32))
+    m.decode_step(None, out)
+    assert rel_err(m.logits(3), ref_logits) < 3e-3
+    with pytest.raises(ob.OnellmError):
+        m.prefill_ragged([np.zeros(200, np.int32), np.zeros(3, np.int32)])  # longer than max_seq_len
+    m.close()
