@@ -9,16 +9,20 @@
 //                         K-major; K by TMA), S in tensor memory (64 columns of fp32, two accumulators so that
 //                         the next tile's product runs under this tile's softmax)
 //   P = exp2(S - ref)     four warps, one query row per thread: the row is read from tensor memory once and kept
-//                         in registers; P goes to shared memory as fp16 in the swizzled K-major form
-//   O += P . V_tile       tcgen05.mma again: P is the A operand, V_tile (rows of the cache, head dimension
-//                         contiguous) is the MN-major B operand, exactly as the [K,N] weights of the projections.
-//                         O stays in tensor memory (128 columns) over all tiles.  `ref` is the row maximum the
-//                         exponentials are taken against; it follows the true running maximum only when that
-//                         has grown by more than 8 (P stays below 2^8), and only then is O rescaled in place.
-// A fifth warp issues the TMA loads (K and V tiles double-buffered) and the MMAs.  112 KB of shared memory and 256
-// columns of tensor memory per block: two blocks share an SM, so one block's start-up and drain hide under the other's steady state.
-// Every mbarrier wait is bounded; on expiry the block raises the time-out flag, stops, frees its tensor memory
-// and returns.
+//                         in registers; P goes back as fp16 (two per 32-bit column) over the first 32 columns of
+//                         the accumulator its scores came from (tcgen05.st)
+//   O += P . V_tile       tcgen05.mma again with the A operand read from tensor memory (no shared-memory copy of P,
+//                         no proxy fence); V_tile (rows of the cache, head dimension contiguous) is the MN-major B
+//                         operand, exactly as the [K,N] weights of the projections.  O stays in tensor memory (128
+//                         columns) over all tiles.  `ref` is the row maximum the exponentials are taken against; it
+//                         follows the true running maximum only when that has grown by more than 8 (P stays below
+//                         2^8), and only then does a thread wait for the previous product and rescale O in place.
+// The MMAs of one thread run in issue order, which is what lets S of tile j + 2 overwrite the accumulator P of tile j
+// was read from without a wait in between.
+// A fifth warp issues the TMA loads (K and V tiles double-buffered) and the MMAs.  96 KB of shared memory and 256
+// columns of tensor memory per block: two blocks share an SM, so one block's start-up and drain hide under the
+// other's steady state.  Every mbarrier wait is bounded; on expiry the block raises the time-out flag, stops, frees
+// its tensor memory and returns.
 #include <math.h>
 
 #include "tc_common.cuh"
@@ -32,12 +36,20 @@ constexpr int kAtQTile = kAtQ * kAtD * 2;           // 32 KB: two 64-column chun
 constexpr int kAtQChunk = kAtQTile / 2;
 constexpr int kAtKVTile = kAtKV * kAtD * 2;         // 16 KB: two 64-column chunks of [64 rows x 128 bytes]
 constexpr int kAtKVChunk = kAtKVTile / 2;
-constexpr int kAtPTile = kAtQ * kAtKV * 2;          // 16 KB: [128 rows x 128 bytes]
-// Q, two K and two V buffers, P, barriers: 112.25 KB, so that two blocks (plus the 1 KB the system keeps per block)
-// fit the 228 KB of an SM; the dynamic array is declared 1024-byte aligned instead of carrying slack for it
-constexpr int kAtSmemBytes = kAtQTile + 4 * kAtKVTile + kAtPTile + 256;
+// Q, two K and two V buffers, barriers: 96.25 KB, two blocks per SM; the dynamic array is declared 1024-byte aligned
+// instead of carrying slack for it
+constexpr int kAtSmemBytes = kAtQTile + 4 * kAtKVTile + 256;
 constexpr uint32_t kAtTmemCols = 256;  // S0 at column 0, S1 at 64, O at 128
 
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand (M rows = lanes, K elements packed two fp16 per 32-bit column) comes
+// from tensor memory
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __global__ void __launch_bounds__(kAtThreads, 2)
@@ -49,8 +61,7 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
     unsigned char* sQ = smem_raw;
     unsigned char* sK = sQ + kAtQTile;       // two buffers
     unsigned char* sV = sK + 2 * kAtKVTile;  // two buffers
-    unsigned char* sP = sV + 2 * kAtKVTile;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kAtPTile);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * kAtKVTile);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), s_full0 = smem_u32(bars + 3), v_full0 = smem_u32(bars + 5),
                    p_full = smem_u32(bars + 7), o_full = smem_u32(bars + 8);
@@ -125,7 +136,7 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
         // Shared-memory descriptors are built once; a step inside a tile only adds (bytes >> 4) to the address field in
         // the low word (the field holds any shared-memory address, so the add never carries out of it).
         const uint64_t dq = umma_desc(smem_u32(sQ), 16, 1024), dk = umma_desc(smem_u32(sK), 16, 1024),
-                       dp = umma_desc(smem_u32(sP), 16, 1024), dv = umma_desc(smem_u32(sV), kAtKVChunk, 1024);
+                       dv = umma_desc(smem_u32(sV), kAtKVChunk, 1024);
         auto issue_s = [&](int j) {  // S_j = Q . K_j^T into accumulator j & 1
             const int s = j & 1;
             if (!wait_all(k_full0 + 8 * s, (uint32_t)(j >> 1) & 1u)) return false;
@@ -169,7 +180,7 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                     // O += P . V_tile.  A = P, K-major over the 64 cache rows of the tile (one 128-byte row per query); B =
                     // V_tile, MN-major: 64-column chunks 8 KB apart (LBO), 8-row groups 1024 bytes apart (SBO), 16 rows =
                     // 2048 bytes further
-                    umma_f16(tmem_base + 128u, dp + (uint64_t)((kk * 32) >> 4), dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
+                    umma_f16_ta(tmem_base + 128u, tmem_base + (uint32_t)(s * kAtKV + kk * 8), dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
                              (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(o_full);
@@ -245,11 +256,11 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l_run += sum;
-            if (j > 0) {
-                ok = mbar_wait(o_full, (uint32_t)(j - 1) & 1u);  // P.V of the tile before: P is free, O is at rest
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                ok = mbar_wait(o_full, (uint32_t)(j - 1) & 1u);  // P.V of the tile before: O is at rest
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                if (__any_sync(0xffffffffu, grow)) {
+                {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t ov[32];
 #pragma unroll 1
@@ -263,14 +274,13 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
             }
-            // P (fp16): 16-byte unit u of the row, XOR-ed with r % 8
+            // P (fp16, two values per 32-bit column) over the first 32 columns of the score accumulator it came from:
+            // the A operand of the P.V product, read from tensor memory
+            {
+                uint32_t pk[32];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                *reinterpret_cast<uint4*>(sP + row_off + ((u ^ (r & 7)) << 4)) =
-                    make_uint4(pack_h2(__uint_as_float(sv[8 * u]), __uint_as_float(sv[8 * u + 1])),
-                               pack_h2(__uint_as_float(sv[8 * u + 2]), __uint_as_float(sv[8 * u + 3])),
-                               pack_h2(__uint_as_float(sv[8 * u + 4]), __uint_as_float(sv[8 * u + 5])),
-                               pack_h2(__uint_as_float(sv[8 * u + 6]), __uint_as_float(sv[8 * u + 7])));
+                for (int i = 0; i < 32; i++) pk[i] = pack_h2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1]));
+                tmem_st32(t_lane + (uint32_t)((j & 1) * kAtKV), pk);
             }
             if (kv0 + kAtKV > kv_end) {
                 // The tile reaches beyond the rows that exist: what the cache holds there is arbitrary (possibly NaN
@@ -283,8 +293,9 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                     for (int u = 0; u < 16; u++)
                         *reinterpret_cast<uint4*>(sV + (j & 1) * kAtKVTile + (u >> 3) * kAtKVChunk + row_off + (u & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
+                fence_async_smem();  // V rows were written through the generic proxy; the MMA reads through the async proxy
             }
-            fence_async_smem();  // P (and V rows) went through the generic proxy; the MMA reads through the async proxy
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_full);
         }
