@@ -59,20 +59,28 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs.
+
+    The nvidia-smi process is started ahead of the warm-up steps, so that its start-up (driver
+    initialisation, which stalls launches on every GPU of the box for tens of milliseconds) is over
+    before the timed region begins; `mark_start` / `mark_end` bracket the timed region and only the
+    samples that arrived between them (plus one period of slack after the end) are summarised.
+    """
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    PERIOD_MS = 200
 
     def __init__(self, index):
         self.rows, self.proc, self.index = [], None, index
+        self.t0 = self.t1 = None
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
+                                          "--format=csv,noheader,nounits", "-lms", str(self.PERIOD_MS)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except OSError:
@@ -81,18 +89,33 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def wait_first(self, timeout_s):
+        t_end = time.perf_counter() + timeout_s
+        while self.proc and not self.rows and time.perf_counter() < t_end:
+            time.sleep(0.01)
+
+    def mark_start(self):
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
 
     def __exit__(self, *a):
         if self.proc:
-            time.sleep(0.15)
+            time.sleep(self.PERIOD_MS * 1e-3 + 0.05)
             self.proc.terminate()
             self.t.join(timeout=2)
 
     def summary(self):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        lo = self.t0 if self.t0 is not None else 0.0
+        hi = (self.t1 if self.t1 is not None else float("inf")) + self.PERIOD_MS * 1e-3
+        for t, r in self.rows:
+            if not (lo <= t <= hi):
+                continue
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -104,7 +127,7 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "period_ms": self.PERIOD_MS}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -292,17 +315,20 @@ def run_ours(args, workload):
         return float(t.item())
 
     # -- device-resident leg: ids never leave the GPU ------------------------------------------
-    for _ in range(W):
-        m.decode_step(None, None)
-    barrier()
-    launches0 = m.state()[1]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
+        clk.wait_first(3.0)  # the sampler's start-up is over before the warm-up, which re-heats the clocks
+        for _ in range(W):
+            m.decode_step(None, None)
+        barrier()
+        launches0 = m.state()[1]
+        clk.mark_start()
         e0.record(stream)
         for _ in range(K):
             m.decode_step(None, None)
         e1.record(stream)
         barrier()
+        clk.mark_end()
     launches = m.state()[1] - launches0
     dev_s = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
     ctx_mid = prompt_len + W + K // 2
