@@ -426,6 +426,12 @@ ONELLM_API int onellm_llama_set_graphs(onellm_llama* m, int enabled);
 ONELLM_API int onellm_llama_p2p_handle(onellm_llama* m, void* handle64);
 ONELLM_API int onellm_llama_p2p_connect(onellm_llama* m, const void* handles);
 ONELLM_API int onellm_llama_p2p_error(onellm_llama* m);
+/* Tensor parallel with peer memory connected: which exchange the decode step uses.  peer_memory != 0 (the
+ * default after onellm_llama_p2p_connect): the projections reduce over peer memory in their own epilogue;
+ * 0: ncclAllReduce on the model's stream, as the context phase does.  Both compute the sum the tensor-parallel
+ * run of src/layers/decoder/self_decoder.cpp:47-73 needs behind o_proj and down_proj; the switch lets a caller
+ * (the benchmark's result check) run the same steps both ways.  Every rank must choose the same. */
+ONELLM_API int onellm_llama_set_tp_exchange(onellm_llama* m, int peer_memory);
 /* 1: run the context phase one position at a time through the decode kernels (cross-check path);
  * 0 (default): all prompt tokens at once through the context-phase kernels. */
 ONELLM_API int onellm_llama_set_prefill_by_decode(onellm_llama* m, int enabled);

@@ -334,6 +334,9 @@ class Llama:
         _check(lib().onellm_llama_set_sampling(self._h, C.c_int(top_k), C.c_float(temperature),
                                                C.c_int(1 if literal_walk else 0)))
 
+    def set_tp_exchange(self, peer_memory: bool):
+        _check(lib().onellm_llama_set_tp_exchange(self._h, C.c_int(1 if peer_memory else 0)))
+
     def set_graphs(self, enabled: bool):
         _check(lib().onellm_llama_set_graphs(self._h, C.c_int(1 if enabled else 0)))
 

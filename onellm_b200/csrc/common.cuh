@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "onellm_b200.h"
 
 namespace onellm {
@@ -48,16 +50,45 @@ long launches_noted();
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Function attributes (cudaFuncSetAttribute), occupancy figures and the SM count belong to a device, not to
+// the process: whatever caches them is indexed by the device the calling thread has current.
+constexpr int kMaxDevices = 64;
+inline int current_device()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+    return dev;
+}
+
+// Runs `f` (returning cudaError_t) the first time it is reached on each device; later calls on that device
+// return cudaSuccess without running it.  One object per call site (a function-local static).
+class DeviceOnce {
+    std::mutex mu_;
+    bool done_[kMaxDevices] = {};
+
+  public:
+    template <typename F>
+    cudaError_t run(F f)
+    {
+        const int dev = current_device();
+        std::lock_guard<std::mutex> lock(mu_);
+        if (done_[dev]) return cudaSuccess;
+        const cudaError_t e = f();
+        if (e == cudaSuccess) done_[dev] = true;
+        return e;
+    }
+};
+
 inline int num_sms()
 {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
+    static int n[kMaxDevices] = {};
+    const int dev = current_device();
+    if (n[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n[dev] = v;
     }
-    return n;
+    return n[dev];
 }
 
 // 16-byte vector of T <-> float registers.

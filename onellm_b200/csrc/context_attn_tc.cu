@@ -62,9 +62,15 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
     unsigned char* sK = sQ + kAtQTile;       // two buffers
     unsigned char* sV = sK + 2 * kAtKVTile;  // two buffers
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * kAtKVTile);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    // Every per-tile barrier comes as a pair: tile j uses slot j & 1 and waits for phase (j >> 1) & 1 of it.  A
+    // parity wait only tells "this phase" from "the next one", so a single barrier would be wrong as soon as its
+    // producer can get two phases ahead of a waiter: the softmax warps may finish tile j + 1 (its scores were issued
+    // before the control warp waits for P of tile j) before a delayed control warp has looked at P of tile j, and
+    // the last P.V product may still be in flight behind the one before it when the softmax warps look for it.
+    // With two slots a slot's next phase (tile j + 2) can only start after its waiter has seen tile j.
     const uint32_t q_full = smem_u32(bars), k_full0 = smem_u32(bars + 1), s_full0 = smem_u32(bars + 3), v_full0 = smem_u32(bars + 5),
-                   p_full = smem_u32(bars + 7), o_full = smem_u32(bars + 8);
+                   p_full0 = smem_u32(bars + 7), o_full0 = smem_u32(bars + 9);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z, h = blockIdx.y, hk = h / (H / Hkv);
 
@@ -78,9 +84,9 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             mbar_init(k_full0 + 8 * s, 1);
             mbar_init(s_full0 + 8 * s, 1);
             mbar_init(v_full0 + 8 * s, 1);
+            mbar_init(p_full0 + 8 * s, kAtSoftmaxThreads);
+            mbar_init(o_full0 + 8 * s, 1);
         }
-        mbar_init(p_full, kAtSoftmaxThreads);
-        mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -170,7 +176,7 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             // K buffer s is free once S_j is complete
             ok = ok && wait_all(s_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
             if (ok && j + 2 < n_tiles) load_k(j + 2);
-            ok = ok && wait_all(p_full, (uint32_t)j & 1u) && wait_all(v_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
+            ok = ok && wait_all(p_full0 + 8 * s, (uint32_t)(j >> 1) & 1u) && wait_all(v_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t dvs = dv + (uint64_t)(s * (kAtKVTile >> 4));
@@ -183,11 +189,11 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
                     umma_f16_ta(tmem_base + 128u, tmem_base + (uint32_t)(s * kAtKV + kk * 8), dvs + (uint64_t)((kk * 2048) >> 4), idesc_o,
                              (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(o_full);
+                umma_commit(o_full0 + 8 * s);
             }
             __syncwarp();
             if (j + 2 < n_tiles) {
-                ok = wait_all(o_full, (uint32_t)j & 1u);  // V buffer s is free again
+                ok = wait_all(o_full0 + 8 * s, (uint32_t)(j >> 1) & 1u);  // V buffer s is free again
                 if (ok) load_v(j + 2);
             }
         }
@@ -257,7 +263,7 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l_run += sum;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                ok = mbar_wait(o_full, (uint32_t)(j - 1) & 1u);  // P.V of the tile before: O is at rest
+                ok = mbar_wait(o_full0 + 8 * ((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u);  // P.V of the tile before: O is at rest
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 {
@@ -297,9 +303,10 @@ context_attn_tc_kernel(const __half* __restrict__ q, long q_ld, const __grid_con
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_full);
+            mbar_arrive(p_full0 + 8 * (j & 1));
         }
-        ok = ok && mbar_wait(o_full, (uint32_t)(n_tiles - 1) & 1u);
+        // the last product; the commit of a product covers every MMA issued before it, the earlier products included
+        ok = ok && mbar_wait(o_full0 + 8 * ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -343,11 +350,8 @@ int context_attn_tc_launch(const __half* q, long q_ld, const __half* k_cache, co
     if (rc) return rc;
     rc = make_map(&map_v, v_cache, (uint64_t)kAtD, (uint64_t)cache_rows, kAtKV);
     if (rc) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        ONELLM_CUDA(cudaFuncSetAttribute(context_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmemBytes));
-        attr_set = true;
-    }
+    static DeviceOnce smem_attr;
+    ONELLM_CUDA(smem_attr.run([] { return cudaFuncSetAttribute(context_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtSmemBytes); }));
     const dim3 grid((max_q_len + kAtQ - 1) / kAtQ, H, B);
     ONELLM_CUDA(launch_pdl(context_attn_tc_kernel, grid, dim3(kAtThreads), kAtSmemBytes, st, q, q_ld, map_k, map_v, cu_seqlens, history, H,
                            Hkv, S_max, scale * 1.4426950408889634f, out));

@@ -789,10 +789,11 @@ struct AttnKernelInfo {
 // Per-kernel facts the planner needs (queried once; also raises the dynamic shared-memory cap).
 static AttnKernelInfo kernel_info(AttnKernel k)
 {
-    static std::map<AttnKernel, AttnKernelInfo> cache;
+    static std::map<std::pair<AttnKernel, int>, AttnKernelInfo> cache;  // per (kernel, device): the attribute is set per device
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(k);
+    const auto key = std::make_pair(k, current_device());
+    auto it = cache.find(key);
     if (it != cache.end()) return it->second;
     AttnKernelInfo info = {4, 4096};
     cudaFuncAttributes fa;
@@ -806,7 +807,7 @@ static AttnKernelInfo kernel_info(AttnKernel k)
                                    (int)(227 * 1024 - fa.sharedSizeBytes));
     }
     (void)cudaGetLastError();
-    cache[k] = info;
+    cache[key] = info;
     return info;
 }
 

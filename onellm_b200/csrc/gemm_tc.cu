@@ -269,15 +269,10 @@ static int gemm_tc_launch(const __half* x, const __half* W, const __half* W2, __
         rc = make_map(&map_b2, W2, (uint64_t)N, (uint64_t)K, kTcBK);
         if (rc) return rc;
     }
-    static bool attr_set[3] = {false, false, false};
-    static std::mutex mu;
+    static DeviceOnce smem_attr[3];
     {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!attr_set[mode]) {
-            const void* fn = mode == 0 ? (const void*)gemm_tc_kernel<0> : mode == 1 ? (const void*)gemm_tc_kernel<1> : (const void*)gemm_tc_kernel<2>;
-            ONELLM_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes));
-            attr_set[mode] = true;
-        }
+        const void* fn = mode == 0 ? (const void*)gemm_tc_kernel<0> : mode == 1 ? (const void*)gemm_tc_kernel<1> : (const void*)gemm_tc_kernel<2>;
+        ONELLM_CUDA(smem_attr[mode].run([fn] { return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes); }));
     }
     const int out_n = mode == 2 ? kTcBN / 2 : kTcBN;
     const long tiles = (long)((N + out_n - 1) / out_n) * ((M + kTcBM - 1) / kTcBM);

@@ -181,6 +181,8 @@ struct Llama {
     size_t attn_ws_bytes = 0;
     onellm_p2p* p2p = nullptr;  // peer-memory all-reduce of the decode step (tensor parallel)
     bool p2p_connected = false;
+    bool use_p2p = true;        // false: keep ncclAllReduce in the decode step although peer memory is connected
+    int* h_comm_err = nullptr;  // pinned: the communicator's error word, copied out at every point the host waits anyway
     // state
     int batch = 0, cur_len = 0, prompt_cap = 0, graph_prompt_len = 0;
     int top_k = 1, literal_walk = 0;
@@ -261,6 +263,7 @@ static void carve(Llama& m, Carver& cv)
 
 static int blocks_for(size_t n) { return (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096); }
 
+const int* p2p_error_word(onellm_p2p* h);  // p2p_allreduce.cu
 int embedding_launch(int dtype, const int* ids, void* out, void* out2, const void* table, int n_tokens, int hidden,
                      int vocab, int* bad_id_flag, bool pdl, cudaStream_t st);
 // sampling.cu
@@ -284,6 +287,26 @@ static int tp_allreduce(Llama& m, __half* buf, size_t n)
     ONELLM_REQUIRE(r == ncclSuccess, ONELLM_ERR_COMM, "ncclAllReduce: %s",
                    nccl_api().GetErrorString ? nccl_api().GetErrorString(r) : "error");
     note_launch();
+    return ONELLM_OK;
+}
+
+// Tensor parallel over peer memory: a rank whose wait for a peer ran out (about a second of SM clocks) has set
+// its communicator's error word and gone on with whatever its receive slot held, so its residual stream, and
+// from there its sampled tokens and cache rows, may differ from the other ranks'.  The engine copies the word
+// out wherever it waits for the stream anyway (queue_comm_check before the wait, comm_check after it) and
+// turns a set word into ONELLM_ERR_COMM.
+static int queue_comm_check(Llama& m)
+{
+    if (!m.p2p_connected || !m.h_comm_err) return ONELLM_OK;
+    ONELLM_CUDA(cudaMemcpyAsync(m.h_comm_err, p2p_error_word(m.p2p), sizeof(int), cudaMemcpyDeviceToHost, m.stream));
+    return ONELLM_OK;
+}
+static int comm_check(Llama& m, const char* where)
+{
+    if (!m.p2p_connected || !m.h_comm_err) return ONELLM_OK;
+    ONELLM_REQUIRE(*m.h_comm_err == 0, ONELLM_ERR_COMM,
+                   "%s: a wait for a tensor-parallel peer ran out (rank %d of %d); the ranks' results may have diverged since",
+                   where, m.c.tp_rank, m.c.tp_size);
     return ONELLM_OK;
 }
 
@@ -338,7 +361,7 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
             RC(onellm_rmsnorm(ONELLM_F16, m.res, m.out_norm, c.rms_eps, B, h, sp));  // in place: the stream ends here
         }
         head_in = m.res;
-    } else if (m.p2p_connected) {
+    } else if (m.p2p_connected && m.use_p2p) {
         // tensor parallel over peer memory: o_proj and down_proj reduce over the ranks in their own epilogue
         // (every finished pair of elements is pushed to the peers and the peers' values gathered) and add
         // the sum, and the bias, into this rank's copy of the residual stream.  Five kernels per layer as on
@@ -674,6 +697,7 @@ extern "C" void onellm_llama_destroy(onellm_llama* h)
     if (m->stream) cudaStreamDestroy(m->stream);
     cudaFree(m->arena);
     if (m->pf_buf) cudaFree(m->pf_buf);
+    if (m->h_comm_err) cudaFreeHost(m->h_comm_err);
     delete m;
 }
 
@@ -872,6 +896,10 @@ extern "C" int onellm_llama_p2p_connect(onellm_llama* h, const void* handles)
     ONELLM_REQUIRE(m && handles, ONELLM_ERR_ARG, "llama_p2p_connect: null pointer");
     ONELLM_REQUIRE(m->p2p, ONELLM_ERR_STATE, "llama_p2p_connect: call onellm_llama_p2p_handle first");
     RC(onellm_p2p_connect(m->p2p, handles));
+    if (!m->h_comm_err) {
+        ONELLM_CUDA(cudaMallocHost(&m->h_comm_err, sizeof(int)));
+        *m->h_comm_err = 0;
+    }
     ONELLM_CUDA(cudaStreamSynchronize(m->stream));
     drop_graphs(*m);
     m->p2p_connected = true;
@@ -882,6 +910,20 @@ extern "C" int onellm_llama_p2p_error(onellm_llama* h)
 {
     Llama* m = reinterpret_cast<Llama*>(h);
     return (m && m->p2p) ? onellm_p2p_error(m->p2p) : 0;
+}
+
+extern "C" int onellm_llama_set_tp_exchange(onellm_llama* h, int peer_memory)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m, ONELLM_ERR_ARG, "llama_set_tp_exchange: null handle");
+    ONELLM_REQUIRE(!peer_memory || m->c.tp_size == 1 || m->p2p_connected, ONELLM_ERR_STATE,
+                   "llama_set_tp_exchange: peer memory is not connected (call onellm_llama_p2p_connect first)");
+    if ((peer_memory != 0) != m->use_p2p) {
+        ONELLM_CUDA(cudaStreamSynchronize(m->stream));
+        drop_graphs(*m);  // the exchange is part of the captured step
+    }
+    m->use_p2p = peer_memory != 0;
+    return ONELLM_OK;
 }
 
 extern "C" int onellm_llama_set_graphs(onellm_llama* h, int enabled)
@@ -926,7 +968,9 @@ extern "C" int onellm_llama_prefill(onellm_llama* h, const int* host_ids, int ba
         RC(prefill_context(*m, batch, lens.data()));
     }
     if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
+    RC(queue_comm_check(*m));
     ONELLM_CUDA(cudaStreamSynchronize(st));
+    RC(comm_check(*m, "llama_prefill"));
     int bad[2] = {0, 0};
     ONELLM_CUDA(cudaMemcpy(bad, m->d_bad_id, 2 * sizeof(int), cudaMemcpyDeviceToHost));
     ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_prefill: token id outside [0, vocab_size)");
@@ -966,7 +1010,9 @@ extern "C" int onellm_llama_prefill_ragged(onellm_llama* h, const int* host_ids,
     ONELLM_CUDA(cudaStreamSynchronize(st));  // `longest` lives on this stack frame
     RC(prefill_context(*m, batch, lens));
     if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
+    RC(queue_comm_check(*m));
     ONELLM_CUDA(cudaStreamSynchronize(st));
+    RC(comm_check(*m, "llama_prefill_ragged"));
     int bad[2] = {0, 0};
     ONELLM_CUDA(cudaMemcpy(bad, m->d_bad_id, 2 * sizeof(int), cudaMemcpyDeviceToHost));
     ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_prefill_ragged: token id outside [0, vocab_size)");
@@ -992,7 +1038,9 @@ extern "C" int onellm_llama_extend(onellm_llama* h, const int* host_ids, int n_n
     const std::vector<int> lens(batch, n_new);
     RC(prefill_context(*m, batch, lens.data()));
     if (host_first_ids) ONELLM_CUDA(cudaMemcpyAsync(host_first_ids, m->d_out_ids, (size_t)batch * sizeof(int), cudaMemcpyDeviceToHost, st));
+    RC(queue_comm_check(*m));
     ONELLM_CUDA(cudaStreamSynchronize(st));
+    RC(comm_check(*m, "llama_extend"));
     int bad[2] = {0, 0};
     ONELLM_CUDA(cudaMemcpy(bad, m->d_bad_id, 2 * sizeof(int), cudaMemcpyDeviceToHost));
     ONELLM_REQUIRE(bad[0] == 0, ONELLM_ERR_ARG, "llama_extend: token id outside [0, vocab_size)");
@@ -1037,7 +1085,9 @@ extern "C" int onellm_llama_decode_step(onellm_llama* h, const int* host_in_ids,
     RC(run_step(*m, MODE_HEAD, 0));
     if (host_out_ids) {
         ONELLM_CUDA(cudaMemcpyAsync(host_out_ids, m->d_out_ids, (size_t)m->batch * sizeof(int), cudaMemcpyDeviceToHost, st));
+        RC(queue_comm_check(*m));
         ONELLM_CUDA(cudaStreamSynchronize(st));
+        RC(comm_check(*m, "llama_decode_step"));
     }
     return ONELLM_OK;
 }
@@ -1046,8 +1096,9 @@ extern "C" int onellm_llama_sync(onellm_llama* h)
 {
     Llama* m = reinterpret_cast<Llama*>(h);
     ONELLM_REQUIRE(m, ONELLM_ERR_ARG, "llama_sync: null handle");
+    RC(queue_comm_check(*m));
     ONELLM_CUDA(cudaStreamSynchronize(m->stream));
-    return ONELLM_OK;
+    return comm_check(*m, "llama_sync");
 }
 
 extern "C" int onellm_llama_generate(onellm_llama* h, const int* host_prompt, int batch, int prompt_len, int n_new, int* host_out)
@@ -1074,10 +1125,12 @@ extern "C" int onellm_llama_get_logits(onellm_llama* h, float* host_logits)
     ONELLM_CUDA(cudaMalloc(&tmp, n * sizeof(float)));
     half_to_float_kernel<<<blocks_for(n), 256, 0, m->stream>>>(m->logits, tmp, n);
     cudaError_t e = cudaMemcpyAsync(host_logits, tmp, n * sizeof(float), cudaMemcpyDeviceToHost, m->stream);
+    const int qrc = queue_comm_check(*m);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     cudaFree(tmp);
     ONELLM_REQUIRE(e == cudaSuccess, ONELLM_ERR_CUDA, "llama_get_logits: %s", cudaGetErrorString(e));
-    return ONELLM_OK;
+    RC(qrc);
+    return comm_check(*m, "llama_get_logits");
 }
 
 extern "C" int onellm_llama_get_state(onellm_llama* h, int* cur_len, long* kernel_launches, int* host_seqlen, unsigned char* host_finished)

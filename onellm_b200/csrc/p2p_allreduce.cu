@@ -295,8 +295,22 @@ extern "C" int onellm_p2p_gemm_allreduce_add(onellm_p2p* h, int dtype, int which
     tp.error = &ctl->error;
     tp.rank = c->rank;
     tp.world = c->world;
-    ONELLM_CUDA(skinny_kn_staged_dispatch((const __half*)x, (const __half*)W, nullptr, (__half*)resid, M, N, K, false,
-                                          reinterpret_cast<cudaStream_t>(stream), (const __half*)resid, (const __half*)bias, -1.f, &tp));
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const cudaError_t e = skinny_kn_staged_dispatch((const __half*)x, (const __half*)W, nullptr, (__half*)resid, M, N, K, false, st,
+                                                    (const __half*)resid, (const __half*)bias, -1.f, &tp);
+    if (e == cudaErrorInvalidConfiguration) {
+        // The exchange inside the projection needs every block of the launch resident at once (a block waits for the
+        // block of the same index on its peers).  A shape whose plan does not fit one wave is refused by the launcher
+        // before anything runs; the same sum is then taken in two kernels: the plain projection into this rank's send
+        // buffer, and the stand-alone exchange.  The plan depends on the shape and the GPU model only, so every rank
+        // takes the same branch.
+        (void)cudaGetLastError();
+        __half* send = static_cast<__half*>(onellm_p2p_send_buffer(h, which));
+        ONELLM_CUDA(skinny_kn_staged_dispatch((const __half*)x, (const __half*)W, nullptr, send, M, N, K, false, st, nullptr, nullptr, -1.f,
+                                              nullptr));
+        return onellm_p2p_allreduce_add(h, dtype, which, resid, bias, M * N, N, stream);
+    }
+    ONELLM_CUDA(e);
     return ONELLM_OK;
 }
 
@@ -311,6 +325,15 @@ extern "C" int onellm_p2p_error(onellm_p2p* h)
     }
     return v;
 }
+
+namespace onellm {
+// device address of the communicator's error word, for callers that read it with their own copy
+const int* p2p_error_word(onellm_p2p* h)
+{
+    P2pComm* c = reinterpret_cast<P2pComm*>(h);
+    return (c && c->local) ? &static_cast<P2pControl*>(c->local)->error : nullptr;
+}
+}  // namespace onellm
 
 extern "C" void onellm_p2p_destroy(onellm_p2p* h)
 {

@@ -381,21 +381,15 @@ extern "C" int onellm_context_attn(int dtype, const void* q, long q_ld, const vo
                                       (long)B * Hkv * (cs_h / D), cu_seqlens, history_length, B, max_q_len, H, Hkv, scale, (__half*)out, st);
     const dim3 grid((max_q_len + kCtxQ - 1) / kCtxQ, H, B);
     const float sl = scale * 1.4426950408889634f;
-    static bool attr64 = false, attr128 = false;
+    static DeviceOnce attr64, attr128;
     if (D == 128) {
         const size_t smem = (size_t)kCtxQ * 256 + 2 * 2 * kCtxKV * 256;
-        if (!attr128) {
-            ONELLM_CUDA(cudaFuncSetAttribute(context_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr128 = true;
-        }
+        ONELLM_CUDA(attr128.run([smem] { return cudaFuncSetAttribute(context_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
         ONELLM_CUDA(launch_pdl(context_attn_kernel<128>, grid, dim3(128), smem, st, (const __half*)q, q_ld, (const __half*)k_cache,
                                (const __half*)v_cache, cs_b, cs_h, cs_s, cu_seqlens, history_length, H, Hkv, sl, (__half*)out));
     } else {
         const size_t smem = (size_t)kCtxQ * 128 + 2 * 2 * kCtxKV * 128;
-        if (!attr64) {
-            ONELLM_CUDA(cudaFuncSetAttribute(context_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr64 = true;
-        }
+        ONELLM_CUDA(attr64.run([smem] { return cudaFuncSetAttribute(context_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }));
         ONELLM_CUDA(launch_pdl(context_attn_kernel<64>, grid, dim3(128), smem, st, (const __half*)q, q_ld, (const __half*)k_cache,
                                (const __half*)v_cache, cs_b, cs_h, cs_s, cu_seqlens, history_length, H, Hkv, sl, (__half*)out));
     }

@@ -451,8 +451,8 @@ static int staged_slots(Kern kern, int ks, int nst, size_t smem, int col_blocks)
 {
     // one table for every instantiation (they share the function-pointer type): the kernel is
     // part of the key
-    static std::map<std::tuple<const void*, int, size_t>, int> cache;
-    const auto key = std::make_tuple((const void*)kern, ks, smem);
+    static std::map<std::tuple<const void*, int, size_t, int>, int> cache;
+    const auto key = std::make_tuple((const void*)kern, ks, smem, current_device());  // occupancy is a per-device figure
     (void)nst;
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
@@ -485,14 +485,13 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     constexpr size_t stage = (size_t)NW * kStageBytes + (FUSED ? 0 : 8 * MB * kXRowBytes);
     constexpr size_t red = ((size_t)NW * 8 * MB * kRedLd + 8 * MB) * sizeof(float);
     constexpr size_t smem_cap = 226 * 1024;
-    static bool attr_set = false;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!attr_set) {
-        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap);
+    static DeviceOnce smem_attr;
+    {
+        const cudaError_t e = smem_attr.run([kern] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap); });
         if (e != cudaSuccess) return e;
-        attr_set = true;
     }
+    static std::mutex mu;  // the occupancy cache below
+    std::lock_guard<std::mutex> lock(mu);
     const int col_blocks = (N + kBN - 1) / kBN;
     const int total_stages = (K + kKC - 1) / kKC;
     // Plan: the K split (= cluster size, 1..8) and ring depth that keep the most bytes in flight

@@ -38,6 +38,13 @@ def random_weights(cfg, seed, std=0.02, attn_bias=False):
     return w
 
 
+# file-name suffix of every per-layer tensor (src/weights/llama/layer_weights.cc:44-54)
+LAYER_FILE_SUFFIX = {"attention_norm": ".attention_norm.weight", "ffn_norm": ".ffn_norm.weight",
+                     "w_qkv": ".attention.w_qkv.weight", "wo": ".attention.wo.weight", "w1": ".feed_forward.w1.weight",
+                     "w3": ".feed_forward.w3.weight", "w2": ".feed_forward.w2.weight", "b_qkv": ".attention.w_qkv.bias",
+                     "b_o": ".attention.wo.bias"}
+
+
 def save_bin(w, prefix, dtype=np.float32):
     """Writes the weights in the reference's on-disk layout: one raw array per tensor, names as in
     src/weights/llama/llama_weights.cc:39-45 and src/weights/llama/layer_weights.cc:44-54."""
@@ -45,13 +52,9 @@ def save_bin(w, prefix, dtype=np.float32):
     w["norm"].astype(dtype).tofile(prefix + ".norm.weight")
     w["tok_embeddings"].astype(dtype).tofile(prefix + ".tok_embeddings.weight")
     w["output"].astype(dtype).tofile(prefix + ".output.weight")
-    names = {"attention_norm": ".attention_norm.weight", "ffn_norm": ".ffn_norm.weight",
-             "w_qkv": ".attention.w_qkv.weight", "wo": ".attention.wo.weight", "w1": ".feed_forward.w1.weight",
-             "w3": ".feed_forward.w3.weight", "w2": ".feed_forward.w2.weight", "b_qkv": ".attention.w_qkv.bias",
-             "b_o": ".attention.wo.bias"}
     for l, lw in enumerate(w["layers"]):
         for k, a in lw.items():
-            a.astype(dtype).tofile(f"{prefix}layers.{l}{names[k]}")
+            a.astype(dtype).tofile(f"{prefix}layers.{l}{LAYER_FILE_SUFFIX[k]}")
 
 
 class LlamaRef:
@@ -112,7 +115,7 @@ class LlamaRef:
 
 def tp_slice(w, cfg, rank, size):
     """The tensor-parallel slice rank `rank` of `size` keeps: query/KV heads and FFN columns, with the
-    matching rows of wo / w2 (the scheme of SURVEY 8e; what the engine's loader cuts from the files)."""
+    matching rows of wo / w2: what the engine's loader cuts from the files."""
     H, Hkv, D, I = cfg["head_num"], cfg["kv_head_num"], cfg["head_size"], cfg["inter_size"]
     Hl, Hkvl, Il = H // size, Hkv // size, I // size
     qs = slice(rank * Hl * D, (rank + 1) * Hl * D)

@@ -48,3 +48,13 @@ def rel_err(got, ref):
     got = np.asarray(got, np.float64)
     ref = np.asarray(ref, np.float64)
     return float(np.max(np.abs(got - ref)) / max(float(np.max(np.abs(ref))), 1e-30))
+
+
+class _DevicePointer:
+    def __init__(self, ptr, n, typestr):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+def device_view(torch, ptr, n, typestr="<f2"):
+    """A torch tensor over `n` elements of device memory the library owns (e.g. the engine's KV cache)."""
+    return torch.as_tensor(_DevicePointer(ptr, n, typestr), device="cuda")

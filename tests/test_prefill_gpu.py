@@ -99,3 +99,35 @@ def test_context_attn_ignores_whatever_lies_behind_the_sequences(ob, cuda, orc, 
     assert np.isfinite(got).all()
     assert rel_err(got, ref) < 1e-3
     assert ob.lib().onellm_gemm_timeout_flag() == 0
+
+
+def test_context_attn_tensor_core_kernel_never_gives_up_a_wait(ob, cuda, orc):
+    """8 sequences x 512 tokens x 32 heads (the context phase of the benchmark), launched 50 times: no block may
+    raise the time-out flag (a block that gives up a bounded wait skips its stores), and the last launch still
+    matches the oracle.  The oracle is run on two of the 32 heads (the per-head arithmetic is identical)."""
+    torch = cuda
+    B, H, D, P = 8, 32, 128, 512
+    rng = np.random.default_rng(5)
+    T, S = B * P, P
+    qkv = _r16(rng.standard_normal((T, 3 * H, D)))
+    kc, vc = _r16(rng.standard_normal((B, H, S, D))), _r16(rng.standard_normal((B, H, S, D)))
+    lens, hist = [P] * B, [0] * B
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    d_qkv = torch.from_numpy(qkv).cuda().half()
+    d_kc, d_vc = torch.from_numpy(kc).cuda().half(), torch.from_numpy(vc).cuda().half()
+    d_cu, d_hist = torch.from_numpy(cu).cuda(), torch.zeros(B, device="cuda", dtype=torch.int32)
+    out = torch.zeros(T, H, D, device="cuda", dtype=torch.float16)
+    ob.lib().onellm_gemm_timeout_flag()  # clear
+    for i in range(50):
+        if i == 49:
+            out.zero_()
+        ob.context_attn(ob.F16, d_qkv, 3 * H * D, d_kc, d_vc, H * S * D, S * D, D, d_cu, d_hist, B, P, H, H, D, D ** -0.5, out)
+        if i % 7 == 0:
+            torch.cuda.synchronize()  # launches both back to back and into an idle GPU
+    torch.cuda.synchronize()
+    assert ob.lib().onellm_gemm_timeout_flag() == 0
+    got = out.float().cpu().numpy()
+    for h in (0, 31):
+        ref = orc.context_attn(np.ascontiguousarray(qkv[:, h:h + 1]), np.ascontiguousarray(kc[:, h:h + 1]),
+                               np.ascontiguousarray(vc[:, h:h + 1]), lens, hist)
+        assert rel_err(got[:, h:h + 1], ref) < 1e-3
