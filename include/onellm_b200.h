@@ -188,6 +188,7 @@ ONELLM_API int onellm_gemm_ld(int dtype, const void* x, const void* W, void* y, 
  * 0 otherwise, -1 if it cannot be read.  Such a block skips its stores: the output is then incomplete. */
 ONELLM_API int onellm_gemm_timeout_flag(void);
 
+
 /* Gate and up projections with SwiGLU applied on the way out:
  *     out[M,I] = silu(x.Wg) * (x.Wu),   Wg, Wu [K,I]
  * Replaces the gate GEMM, up GEMM and launchAct of LLaMAFFNLayer::forward

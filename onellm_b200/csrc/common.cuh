@@ -79,6 +79,13 @@ class DeviceOnce {
     }
 };
 
+// Every kernel of a decode step asks for the same L1 / shared-memory split (the largest shared memory).  An SM
+// changes its split only while it is idle: a kernel that follows one with a different split finds the old split
+// on every SM that still holds a block, fits fewer of its own blocks there, and a launch planned for one wave runs
+// in two (measured on B200: the 33 MB o_proj behind the decode attention took 20 us instead of 10).
+// Call before launching `kernel`; the attribute is set once per (kernel, device).
+cudaError_t prefer_max_shared(const void* kernel);
+
 inline int num_sms()
 {
     static int n[kMaxDevices] = {};
@@ -201,6 +208,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     note_launch();
+    (void)prefer_max_shared(reinterpret_cast<const void*>(kernel));  // one L1 / shared-memory split for every kernel of a step
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -805,6 +805,7 @@ static AttnKernelInfo kernel_info(AttnKernel k)
         info.blocks_per_sm_regs = by_regs;
         (void)cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(227 * 1024 - fa.sharedSizeBytes));
+        (void)prefer_max_shared((const void*)k);  // same L1 / shared-memory split as the projections around it
     }
     (void)cudaGetLastError();
     cache[key] = info;

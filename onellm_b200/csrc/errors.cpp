@@ -2,7 +2,11 @@
 #include <stdarg.h>
 #include <stdio.h>
 
-#include "onellm_b200.h"
+#include <mutex>
+#include <set>
+#include <utility>
+
+#include "common.cuh"
 
 namespace onellm {
 
@@ -21,6 +25,18 @@ void set_error(const char* fmt, ...)
 static thread_local long g_launches = 0;
 void note_launch(int n) { g_launches += n; }
 long launches_noted() { return g_launches; }
+
+cudaError_t prefer_max_shared(const void* kernel)
+{
+    static std::mutex mu;
+    static std::set<std::pair<const void*, int>> done;
+    const auto key = std::make_pair(kernel, current_device());
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.count(key)) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) done.insert(key);
+    return e;
+}
 
 }  // namespace onellm
 

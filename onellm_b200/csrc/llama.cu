@@ -322,6 +322,8 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
     // launched with full stream dependencies; every later kernel of the step may overlap its
     // predecessor's tail (programmatic dependent launch) and therefore starts after these.
     note_launch();
+    (void)prefer_max_shared((const void*)advance_step_kernel);  // same L1 / shared-memory split as every kernel behind it
+    (void)prefer_max_shared((const void*)gather_prompt_ids_kernel);
     advance_step_kernel<<<1, 1, 0, st>>>(m.d_step);
     if (mode & MODE_GATHER) {
         note_launch();

@@ -452,10 +452,14 @@ static int staged_slots(Kern kern, int ks, int nst, size_t smem, int col_blocks)
     // one table for every instantiation (they share the function-pointer type): the kernel is
     // part of the key
     static std::map<std::tuple<const void*, int, size_t, int>, int> cache;
+    static std::mutex cache_mu;  // the planners of different instantiations reach this table under their own locks
     const auto key = std::make_tuple((const void*)kern, ks, smem, current_device());  // occupancy is a per-device figure
     (void)nst;
-    auto it = cache.find(key);
-    if (it != cache.end()) return it->second;
+    {
+        std::lock_guard<std::mutex> lock(cache_mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) return it->second;
+    }
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -472,13 +476,20 @@ static int staged_slots(Kern kern, int ks, int nst, size_t smem, int col_blocks)
         (void)cudaGetLastError();
         clusters = num_sms() / ks;
     }
+    std::lock_guard<std::mutex> lock(cache_mu);
     cache[key] = clusters * ks;
     return clusters * ks;
 }
 
+// Launch plan of one projection shape: K split (= cluster size), ring depth, stages per block.
+struct StagedPlan {
+    int ks, nst, per_block;
+    size_t smem;
+    cudaError_t status;  // cudaErrorInvalidConfiguration: the tensor-parallel epilogue was asked for and no plan fits one wave
+};
+
 template <int MB, bool DUAL, bool FUSED>
-static cudaError_t launch_staged(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K,
-                                 const FusedNormArgs& fn, const EpilogueArgs& ep, cudaStream_t st)
+static StagedPlan plan_staged(int N, int K, bool tp)
 {
     auto kern = skinny_kn_staged_kernel<MB, DUAL, FUSED>;
     constexpr int NW = DUAL ? 2 : 1;
@@ -486,69 +497,87 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     constexpr size_t red = ((size_t)NW * 8 * MB * kRedLd + 8 * MB) * sizeof(float);
     constexpr size_t smem_cap = 226 * 1024;
     static DeviceOnce smem_attr;
-    {
-        const cudaError_t e = smem_attr.run([kern] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap); });
+    StagedPlan plan = {1, 3, 0, 0, cudaSuccess};
+    plan.status = smem_attr.run([kern] {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_cap);
         if (e != cudaSuccess) return e;
-    }
-    static std::mutex mu;  // the occupancy cache below
+        return prefer_max_shared((const void*)kern);
+    });
+    if (plan.status != cudaSuccess) return plan;
+    static std::mutex mu;  // the plan and occupancy caches
     std::lock_guard<std::mutex> lock(mu);
+    static std::map<std::tuple<int, int, bool, int>, StagedPlan> plans;  // one table per instantiation
+    const auto key = std::make_tuple(N, K, tp, current_device());
+    auto it = plans.find(key);
+    if (it != plans.end()) return it->second;
     const int col_blocks = (N + kBN - 1) / kBN;
     const int total_stages = (K + kKC - 1) / kKC;
-    // Plan: the K split (= cluster size, 1..8) and ring depth that keep the most bytes in flight
+    // The K split (= cluster size, 1..8) and ring depth that keep the most bytes in flight
     // while every block is resident at once (residency asked from the runtime, because clusters
     // do not always pack the SMs of a GPC fully).  A sweep over (split, depth) on B200 for the
     // four projection shapes of the 7B model agrees with this rule within a microsecond.
     int best_ks = 1, best_nst = 3;
-    {
-        double best_inflight = -1.0;
-        for (int ks = 1; ks <= 8; ks++) {
-            const int per = (total_stages + ks - 1) / ks;
-            if (ks > 1 && per < 4) break;
-            const long total = (long)col_blocks * ks;
-            const size_t xn_b = FUSED ? (size_t)8 * MB * (per * kKC + 8) * sizeof(__half) : 0;
-            for (int nst = std::min(12, std::max(3, per + 1)); nst >= 3; nst--) {
-                const size_t smem = std::max(stage * nst, red) + xn_b;
-                if (smem > smem_cap) continue;
-                if (staged_slots(kern, ks, nst, smem, col_blocks) < total) continue;
-                // FUSED: every block redoes the row statistics, so fewer blocks are better there
-                const double inflight = (double)total * (nst - 1) * (double)(NW * kStageBytes) / (FUSED ? (double)ks : 1.0);
-                if (inflight > best_inflight * 1.02) {
-                    best_inflight = inflight;
-                    best_ks = ks;
-                    best_nst = nst;
-                }
-                break;  // shallower rings for this split only lose
+    double best_inflight = -1.0;
+    for (int ks = 1; ks <= 8; ks++) {
+        const int per = (total_stages + ks - 1) / ks;
+        if (ks > 1 && per < 4) break;
+        const long total = (long)col_blocks * ks;
+        const size_t xn_b = FUSED ? (size_t)8 * MB * (per * kKC + 8) * sizeof(__half) : 0;
+        for (int nst = std::min(12, std::max(3, per + 1)); nst >= 3; nst--) {
+            const size_t smem = std::max(stage * nst, red) + xn_b;
+            if (smem > smem_cap) continue;
+            if (staged_slots(kern, ks, nst, smem, col_blocks) < total) continue;
+            // FUSED: every block redoes the row statistics, so fewer blocks are better there
+            const double inflight = (double)total * (nst - 1) * (double)(NW * kStageBytes) / (FUSED ? (double)ks : 1.0);
+            if (inflight > best_inflight * 1.02) {
+                best_inflight = inflight;
+                best_ks = ks;
+                best_nst = nst;
             }
-        }
-        if (best_inflight < 0) {  // nothing fits in one wave: smallest blocks, shallow ring
-            // (not for the tensor-parallel epilogue: its blocks wait for their peers on other GPUs, which is
-            // only free of deadlock when every block of the launch is resident)
-            if (ep.tp.world > 1) return cudaErrorInvalidConfiguration;
-            best_ks = 1;
-            best_nst = 3;
+            break;  // shallower rings for this split only lose
         }
     }
-    const int per_block_final = (total_stages + best_ks - 1) / best_ks;
-    const size_t xn_final = FUSED ? (size_t)8 * MB * (per_block_final * kKC + 8) * sizeof(__half) : 0;
-    const size_t smem_final = std::max(stage * best_nst, red) + xn_final;
-    if (smem_final > smem_cap) return cudaErrorInvalidConfiguration;
-    if (ep.tp.world > 1 && (long)col_blocks * best_ks > kTpMaxBlocks) return cudaErrorInvalidConfiguration;
+    if (best_inflight < 0) {  // nothing fits in one wave: smallest blocks, shallow ring
+        // (not for the tensor-parallel epilogue: its blocks wait for their peers on other GPUs, which is
+        // only free of deadlock when every block of the launch is resident)
+        if (tp) plan.status = cudaErrorInvalidConfiguration;
+        best_ks = 1;
+        best_nst = 3;
+    }
+    plan.ks = best_ks;
+    plan.nst = best_nst;
+    plan.per_block = (total_stages + best_ks - 1) / best_ks;
+    const size_t xn_final = FUSED ? (size_t)8 * MB * (plan.per_block * kKC + 8) * sizeof(__half) : 0;
+    plan.smem = std::max(stage * best_nst, red) + xn_final;
+    if (plan.status == cudaSuccess && plan.smem > smem_cap) plan.status = cudaErrorInvalidConfiguration;
+    if (plan.status == cudaSuccess && tp && (long)col_blocks * best_ks > kTpMaxBlocks) plan.status = cudaErrorInvalidConfiguration;
+    plans[key] = plan;
+    return plan;
+}
+
+template <int MB, bool DUAL, bool FUSED>
+static cudaError_t launch_staged(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K,
+                                 const FusedNormArgs& fn, const EpilogueArgs& ep, cudaStream_t st)
+{
+    auto kern = skinny_kn_staged_kernel<MB, DUAL, FUSED>;
+    const StagedPlan plan = plan_staged<MB, DUAL, FUSED>(N, K, ep.tp.world > 1);
+    if (plan.status != cudaSuccess) return plan.status;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = best_ks;
+    attr[0].val.clusterDim.y = plan.ks;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.gridDim = dim3(col_blocks, best_ks, 1);
+    cfg.gridDim = dim3((N + kBN - 1) / kBN, plan.ks, 1);
     cfg.blockDim = dim3(kStThreads);
-    cfg.dynamicSmemBytes = smem_final;
+    cfg.dynamicSmemBytes = plan.smem;
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     note_launch();
-    return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, per_block_final, best_nst, fn, ep);
+    return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, plan.per_block, plan.nst, fn, ep);
 }
 
 // One pass of at most 64 tokens.  Called from skinny_gemm.cu.

@@ -12,6 +12,8 @@ Decode-step cases (HBM-bound, reported in GB/s of algorithmic bytes):
     norm, rmsnorm                  fused add-residual RMSNorm / RMSNorm on 4096 x hidden fp16
     norm8                          the same on --batch rows
     topk, sample                   top-K (K = 50) over [batch, vocab] fp16 logits / the sampler behind it
+    decode_layer                   the five kernels of one decoder layer in the decode step's order (QKV, attention, o_proj,
+                                   gate/up, down); with --graph: the layer as the decode step runs it
 Context-phase cases (reported in TFLOP/s, except prefill_rope):
     prefill_qkv, prefill_o, prefill_gate, prefill_down, prefill_lm     projections on --batch x --ctx token rows
     prefill_attn                   causal attention of --batch sequences x --ctx tokens
@@ -37,7 +39,7 @@ MODELS = {
 }
 
 DECODE_CASES = ["qkv", "o_proj", "gate_up", "down", "lm_head_kn", "lm_head", "attn", "attn_c1", "norm", "rmsnorm", "norm8",
-                "topk", "sample"]
+                "topk", "sample", "decode_layer"]
 PREFILL_CASES = ["prefill_qkv", "prefill_o", "prefill_gate", "prefill_down", "prefill_lm", "prefill_attn", "prefill_rope",
                  "prefill_layer"]
 
@@ -156,6 +158,31 @@ def make_case(name, torch, model="7b", batch=8, ctx=2040, tp=1, plain=False) -> 
         out = torch.empty(B, device="cuda", dtype=torch.int32)
         fn = lambda i: ob.topk_sample(idx, val, B, 50, 1.0, 7 + i, V, 2, out)
         return Case(fn, rot, B * 50 * 8 + B * 4, "B", "sample_kernel", keep=(lg, val, idx, out))
+
+    if name == "decode_layer":
+        S = ctx + 8
+        rot = 2
+        w_qkv, w_o = [rnd(HID, 3 * H * D) for _ in range(rot)], [rnd(H * D, HID) for _ in range(rot)]
+        w_g, w_u, w_d = [rnd(HID, INTER) for _ in range(rot)], [rnd(HID, INTER) for _ in range(rot)], [rnd(INTER, HID) for _ in range(rot)]
+        kc = [torch.randn(B, H, S, D, **half) for _ in range(rot)]
+        vc = [torch.randn(B, H, S, D, **half) for _ in range(rot)]
+        res, qkv = act(B, HID), torch.empty(B, 3 * H, D, **half)
+        o, a = torch.empty(B, H * D, **half), torch.empty(B, INTER, **half)
+        wsb = ob.decode_attn_workspace_bytes(B, H, D, S)
+        ws = torch.empty(wsb, device="cuda", dtype=torch.uint8)
+        p, step = qkv.data_ptr(), ctx + 1
+
+        def fn(i):
+            ob.gemm_fused(F16, res, w_qkv[i], None, qkv, B, 3 * H * D, HID, 1e-5, None, None)
+            ob.decode_attn(F16, p, p + H * D * 2, p + 2 * H * D * 2, 3 * H * D, 3 * H * D, 3 * H * D, None, None, None, kc[i], vc[i],
+                           H * S * D, S * D, D, B, H, H, D, step, step - 1, D, 10000.0, D ** -0.5, o, H * D, ws, wsb)
+            ob.gemm_fused(F16, o, w_o[i], None, res, B, HID, H * D, -1.0, res, None)
+            ob.gemm_fused(F16, res, w_g[i], w_u[i], a, B, INTER, HID, 1e-5, None, None)
+            ob.gemm_fused(F16, a, w_d[i], None, res, B, HID, INTER, -1.0, res, None)
+
+        nbytes = (HID * 3 * H * D + H * D * HID + 3 * HID * INTER) * 2 + 2 * ctx * B * H * D * 2
+        return Case(fn, rot, nbytes, "B", "skinny_kn_staged_kernel + decode_attn_mma_kernel", launches=5,
+                    keep=(w_qkv, w_o, w_g, w_u, w_d, kc, vc, res, qkv, o, a, ws))
 
     # ---- context phase: --batch sequences of --ctx new tokens each ---------------------------------------
     P = ctx

@@ -487,3 +487,4 @@ def test_gemm_f16_tensor_core_tiles(ob, cuda, orc, M, N, K, nk):
     torch.cuda.synchronize()
     assert ob.lib().onellm_gemm_timeout_flag() == 0
     assert rel_err(y.float().cpu().numpy(), orc.gemm(x, W, w_is_nk=nk)) < TOL["f16"]
+
