@@ -188,6 +188,25 @@ ONELLM_API int onellm_gemm_ld(int dtype, const void* x, const void* W, void* y, 
  * 0 otherwise, -1 if it cannot be read.  Such a block skips its stores: the output is then incomplete. */
 ONELLM_API int onellm_gemm_timeout_flag(void);
 
+/* Tuning aids for the weight-streaming projections (at most 64 tokens, [K, N] weights; no counterpart in the
+ * reference, whose GEMMs go to cuBLAS, src/kernels/qkv_linear.cu:8-65).  A launch is planned once per shape:
+ * the K range is split over the blocks of a thread-block cluster (k_split, 1..8) and every block streams its
+ * rows through a shared-memory ring of ring_depth stages.  onellm_gemm_plan_query reports the plan a shape
+ * gets (dual != 0: gate/up with two weight matrices) and the thread blocks it launches;
+ * onellm_gemm_plan_override forces one for every later launch of that shape in this process (k_split 0
+ * removes it).  A forced plan that does not fit shared memory makes those launches fail with ONELLM_ERR_CUDA;
+ * the tensor-parallel kernel onellm_p2p_gemm_allreduce_add ignores overrides. */
+ONELLM_API int onellm_gemm_plan_query(int M, int N, int K, int dual, int* k_split, int* ring_depth, int* blocks);
+ONELLM_API int onellm_gemm_plan_override(int N, int K, int dual, int k_split, int ring_depth);
+/* Projections of [min_tokens, 64] tokens with [K, N] weights run on the tcgen05 weight-streaming kernel, fewer
+ * tokens on the mma.sync one (default 33).  Sets the threshold (min_tokens >= 1; 65 or more: never) and returns
+ * the value it had; min_tokens <= 0 only queries.  A tuning aid like the two calls above. */
+ONELLM_API int onellm_gemm_tc_min_tokens(int min_tokens);
+/* The same kind of aid for the fp16 decode attention (head size 64 / 128): forces the thread blocks per SM (1..3,
+ * which fixes the depth of the per-warp rings) and / or the number of row ranges a (sequence, head) pair is split
+ * into (1..16) for every later launch in this process; 0 leaves the choice to the planner. */
+ONELLM_API int onellm_decode_attn_plan_override(int blocks_per_sm, int splits);
+
 
 /* Gate and up projections with SwiGLU applied on the way out:
  *     out[M,I] = silu(x.Wg) * (x.Wu),   Wg, Wu [K,I]

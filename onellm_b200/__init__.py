@@ -147,6 +147,25 @@ def add_residual_rmsnorm_gemm(dtype, x, residual, bias, gamma, eps, residual_out
                                                   C.c_int(N), C.c_int(K), _stream(stream)))
 
 
+def gemm_plan_query(M, N, K, dual=False):
+    """(k_split, ring_depth, blocks) of the launch plan of a weight-streaming projection."""
+    ks, nst, blocks = C.c_int(0), C.c_int(0), C.c_int(0)
+    _check(lib().onellm_gemm_plan_query(C.c_int(M), C.c_int(N), C.c_int(K), C.c_int(1 if dual else 0), C.byref(ks),
+                                        C.byref(nst), C.byref(blocks)))
+    return ks.value, nst.value, blocks.value
+
+
+def gemm_plan_override(N, K, dual, k_split, ring_depth=12):
+    """Forces the launch plan of a projection shape (k_split 0 removes the override)."""
+    _check(lib().onellm_gemm_plan_override(C.c_int(N), C.c_int(K), C.c_int(1 if dual else 0), C.c_int(k_split),
+                                           C.c_int(ring_depth)))
+
+
+def gemm_tc_min_tokens(min_tokens=0):
+    """Sets (min_tokens >= 1) or queries the token count from which projections use the tcgen05 kernel."""
+    return int(lib().onellm_gemm_tc_min_tokens(C.c_int(min_tokens)))
+
+
 def swiglu(dtype, inp, out, tokens, inter, stream=None):
     _check(lib().onellm_swiglu(C.c_int(dtype), _p(inp), _p(out), C.c_int(tokens), C.c_int(inter),
                                _stream(stream)))

@@ -706,9 +706,19 @@ static AttnPlan plan_attention(int B, int n_head_blocks, int step, int regs_per_
     return best;
 }
 
-// Plan for the tensor-core kernel: blocks per SM r in {3, 2, 1} fix the ring depth shared memory
-// allows (2, 3, 6 stages per warp at D = 128); the splits fill r * SMs block slots; the choice is
-// the one with the most bytes in flight among those that need a single wave.
+// Plan for the tensor-core kernel: blocks per SM r in {3, 2, 1} fix the ring depth shared memory allows (2, 3, 6
+// stages per warp at D = 128).  For every split count the launch's time is estimated from what was measured
+// to bound it on B200:
+//   - a warp takes its tiles one after the other, so with `depth` tiles in flight it moves at most
+//     depth * tile / latency (latency under load about 2.3 us): shallow rings need many resident warps;
+//   - a warp needs about 0.9 us of issue time per 16-row tile (D = 128), and an SM gains little beyond 8 warps:
+//     one block per SM cannot reach the HBM rate however deep its ring is;
+//   - the blocks should fill the waves they need, each wave has a fixed cost (q, RoPE, the warps' merge), and a
+//     split launch pays for the merge kernel behind it.
+// Many (sequence, head) pairs on few slots, e.g. 320 pairs per GPU of an 8-way split 13B model at batch 64, are
+// split so that the last wave is full instead of running one shallow ring per pair.
+static int g_plan_force_r = 0, g_plan_force_n = 0;  // onellm_decode_attn_plan_override (tuning aid)
+
 static AttnPlan plan_attention_mma(int B, int n_head_blocks, int step, int D, int regs_per_sm)
 {
     const int n_cached = step > 1 ? step - 1 : 0;
@@ -716,34 +726,52 @@ static AttnPlan plan_attention_mma(int B, int n_head_blocks, int step, int D, in
     const int ms = max_splits(step);
     const int sms = num_sms();
     const size_t tile = (size_t)2 * kMmaTileRows * D * 2;
+    const int rows_all = (n_cached + 63) / 64 * 64 < kMinChunkRows ? kMinChunkRows : (n_cached + 63) / 64 * 64;
     // fallback (never taken while any ring fits): one split over all rows, two stages
-    AttnPlan best = {1, (n_cached + 63) / 64 * 64 < kMinChunkRows ? kMinChunkRows : (n_cached + 63) / 64 * 64, 2,
-                     2 * kMmaWarps * tile};
-    double best_score = -1.0e300;  // scores may be negative (the merge penalty)
+    AttnPlan best = {1, rows_all, 2, 2 * kMmaWarps * tile};
+    double best_t = 1.0e300;
+    const double bytes = 2.0 * (double)n_cached * (double)base * D * 2.0;
+    constexpr double kPeak = 6.5e12, kLatency = 2.3e-6, kWaveCost = 1.0e-6, kMergeCost = 3.0e-6;
+    const double t_tile = 0.9e-6 * (double)D / 128.0;
+    // Two blocks per SM (three stages per warp at D = 128) won or tied every sweep over (blocks per SM, splits) on B200,
+    // from 32 to 2560 (sequence, head) pairs and 520 to 2040 rows: three blocks leave one tile in flight per warp, one
+    // block has too few warps to issue.  The other values are only tried on request or when two blocks do not fit.
+    const int r_default = regs_per_sm >= 2 ? 2 : 1;
     for (int r = regs_per_sm < 3 ? regs_per_sm : 3; r >= 1; r--) {
+        if (r != (g_plan_force_r > 0 ? g_plan_force_r : r_default)) continue;
         const size_t budget = (size_t)(227 * 1024) / r - 4096;
         int nst = (int)(budget / (kMmaWarps * tile));
         if (nst > 8) nst = 8;
         if (nst < 2) continue;
         const long slots = (long)r * sms;
-        long n = slots / base;
-        if (n < 1) n = 1;
-        if (n > ms) n = ms;
-        int c = (int)((n_cached + n - 1) / n);
-        c = (c + 63) / 64 * 64;  // whole tiles for each of the four warps
-        if (c < kMinChunkRows) c = kMinChunkRows;
-        int ns = (n_cached + c - 1) / c;
-        if (ns < 1) ns = 1;
-        const long total = base * ns;
-        const long waves = (total + slots - 1) / slots;
-        const long resident = total < slots ? total : slots;
-        const int tiles_per_warp = (c / kMmaWarps + kMmaTileRows - 1) / kMmaTileRows;
-        const int depth = nst - 1 < tiles_per_warp ? nst - 1 : tiles_per_warp;
-        const double inflight = (double)resident * kMmaWarps * depth * (double)tile;
-        const double score = inflight / (double)waves - (ns > 1 ? 1.0e6 : 0.0);  // a merge kernel costs a little
-        if (score > best_score) {
-            best_score = score;
-            best = {ns, c, nst, (size_t)nst * kMmaWarps * tile};
+        int last_ns = 0;
+        for (int n = 1; n <= ms && n <= 16; n++) {
+            if (g_plan_force_n > 0 && n != g_plan_force_n) continue;
+            int c = (n_cached + n - 1) / n;
+            c = (c + 63) / 64 * 64;  // whole tiles for each of the four warps
+            if (c < kMinChunkRows) c = kMinChunkRows;
+            int ns = (n_cached + c - 1) / c;
+            if (ns < 1) ns = 1;
+            if (ns == last_ns) continue;  // the same launch as the split count before
+            last_ns = ns;
+            const long total = base * ns;
+            const long waves = (total + slots - 1) / slots;
+            const long resident = total < slots ? total : slots;
+            const double fill = total <= slots ? 1.0 : (double)total / (double)(waves * slots);
+            const int tiles_per_warp = (c / kMmaWarps + kMmaTileRows - 1) / kMmaTileRows;
+            const int depth = nst - 1 < tiles_per_warp ? nst - 1 : tiles_per_warp;
+            const double by_latency = (double)resident * kMmaWarps * depth * (double)tile / kLatency;
+            const long sms_used = (resident + r - 1) / r < sms ? (resident + r - 1) / r : sms;
+            const int warps_sm = r * kMmaWarps < 8 ? r * kMmaWarps : 8;
+            const double by_issue = (double)sms_used * warps_sm * (double)tile / t_tile;
+            double rate = kPeak * fill;
+            if (by_latency < rate) rate = by_latency;
+            if (by_issue < rate) rate = by_issue;
+            const double t = bytes / rate + kWaveCost * (double)waves + (ns > 1 ? kMergeCost : 0.0);
+            if (t < best_t) {
+                best_t = t;
+                best = {ns, c, nst, (size_t)nst * kMmaWarps * tile};
+            }
         }
     }
     return best;
@@ -815,6 +843,15 @@ static AttnKernelInfo kernel_info(AttnKernel k)
 }  // namespace onellm
 
 using namespace onellm;
+
+extern "C" int onellm_decode_attn_plan_override(int blocks_per_sm, int splits)
+{
+    ONELLM_REQUIRE(blocks_per_sm >= 0 && blocks_per_sm <= 3 && splits >= 0 && splits <= 16, ONELLM_ERR_ARG,
+                   "decode_attn_plan_override: blocks per SM in 0..3, splits in 0..16 (0 = the planner decides)");
+    g_plan_force_r = blocks_per_sm;
+    g_plan_force_n = splits;
+    return ONELLM_OK;
+}
 
 extern "C" size_t onellm_decode_attn_workspace_bytes(int B, int H, int D, int max_step)
 {

@@ -299,12 +299,13 @@ int gemm_swiglu_f16_large(const __half* x, const __half* Wg, const __half* Wu, _
 }
 
 int attn_tc_timeout_flag();  // context_attn_tc.cu
+int skinny_tc_flag();         // skinny_gemm_tc.cu
 
 // 1 when a tensor-core block (projection or context attention) gave up a bounded wait since the last call.
 int gemm_tc_timeout_flag()
 {
-    const int a = tc_flag_read_clear(), b = attn_tc_timeout_flag();
-    return (a < 0 || b < 0) ? -1 : (a | b);
+    const int a = tc_flag_read_clear(), b = attn_tc_timeout_flag(), c = skinny_tc_flag();
+    return (a < 0 || b < 0 || c < 0) ? -1 : (a | b | c);
 }
 
 }  // namespace onellm

@@ -252,6 +252,27 @@ extern "C" int onellm_gemm(int dtype, const void* x, const void* W, void* y, int
     return onellm_gemm_ld(dtype, x, W, y, N, M, N, K, w_layout, stream);
 }
 
+namespace onellm {
+cudaError_t staged_plan_query(int M, int N, int K, bool dual, int* ks, int* nst, int* blocks);
+void staged_plan_override(int N, int K, bool dual, int ks, int nst);
+}  // namespace onellm
+
+extern "C" int onellm_gemm_plan_query(int M, int N, int K, int dual, int* k_split, int* ring_depth, int* blocks)
+{
+    ONELLM_REQUIRE(M >= 1 && M <= 64 && N > 0 && K > 0 && K % 16 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED,
+                   "gemm_plan_query: covers the fp16 projections of at most 64 tokens with [K, N] weights");
+    ONELLM_CUDA(staged_plan_query(M, N, K, dual != 0, k_split, ring_depth, blocks));
+    return ONELLM_OK;
+}
+
+extern "C" int onellm_gemm_plan_override(int N, int K, int dual, int k_split, int ring_depth)
+{
+    ONELLM_REQUIRE(N > 0 && K > 0 && k_split <= 8 && (k_split <= 0 || ring_depth >= 3), ONELLM_ERR_ARG,
+                   "gemm_plan_override: K split in 1..8 (0 removes the override), ring depth >= 3");
+    staged_plan_override(N, K, dual != 0, k_split, ring_depth);
+    return ONELLM_OK;
+}
+
 extern "C" int onellm_gemm_fused(int dtype, const void* x, const void* W, const void* Wu, void* y, int M, int N, int K,
                                  float rms_eps, const void* resid, const void* bias, void* stream)
 {

@@ -26,17 +26,13 @@
 #include <tuple>
 #include <utility>
 
-#include "common.cuh"
-
-namespace cg = cooperative_groups;
+#include "skinny_common.cuh"
 
 namespace onellm {
 
 constexpr int kStThreads = 256;
-constexpr int kBN = 128;                 // columns per block
 constexpr int kKC = 32;                  // rows per stage
 constexpr int kStageBytes = kKC * kBN * 2;  // 8 KB per weight matrix
-constexpr int kRedLd = kBN + 1;
 constexpr int kXRowBytes = kKC * 2 + 16;   // activation rows of a stage, padded: conflict-free fragment reads
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr)
@@ -69,21 +65,6 @@ struct FusedNormArgs {
     const __half* gamma;     // [K]
     __half* residual_out;    // [M, K], must not alias residual (other blocks still read it); NULL when x is NULL
     float eps;
-};
-
-// Options of the plain (not FUSED) kernel that let a decoder layer run without norm kernels:
-//   rms:   the result is scaled per token by rsqrt(mean_over_K(x^2) + rms_eps), i.e. the projection of
-//          RMSNorm(x) when the norm's gamma has been multiplied into the rows of W beforehand.  The sum
-//          of squares is taken from the activations as they pass through the ring (no extra reads).
-//   resid: y = resid + bias + result (bias may be NULL); resid may be y itself (each element is read
-//          and written by the same thread).
-struct EpilogueArgs {
-    const __half* resid;  // [M, N] or NULL
-    const __half* bias;   // [N] or NULL
-    float rms_eps;
-    int rms;
-    int early_dependents;  // release the next kernel before the main loop (it then shares the SM with this one)
-    TpEpilogue tp;         // tensor parallel: y = resid + bias + sum over ranks of this projection (see common.cuh)
 };
 
 template <int MB, bool DUAL, bool FUSED>
@@ -345,103 +326,7 @@ skinny_kn_staged_kernel(const __half* __restrict__ x, const __half* __restrict__
             if (t == 0) red_ss[8 * mb + g] = v;
         }
     }
-    // tensor parallel: this block's sequence number for the call (blocks pair up by index across the ranks)
-    __shared__ uint32_t s_seq;
-    const bool tp = !FUSED && ep.tp.world > 1;
-    if (tp && tid == 0) {
-        int* ctr = ep.tp.counters + blockIdx.y * gridDim.x + blockIdx.x;
-        const int n = *ctr + 1;
-        *ctr = n;
-        s_seq = 0x80000000u | (uint32_t)n;  // the high bit keeps these apart from the numbers of the stand-alone all-reduce
-    }
-    cluster.sync();
-    const uint32_t seq = tp ? s_seq : 0u;
-    // every rank of the cluster finishes an even-sized slice of the tile, two adjacent columns per thread
-    const int per_rank = (((MP * kBN + KS - 1) / KS) + 1) & ~1;
-    const int e_begin = rank * per_rank, e_end = min(e_begin + per_rank, MP * kBN);
-    const long long t_start = clock64();
-    for (int e = e_begin + 2 * tid; e < e_end; e += 2 * kStThreads) {
-        const int tok = e / kBN, c = e % kBN;
-        // all remote loads are issued before the first is used (a cluster has at most 8 ranks): summing as
-        // they are requested would pay one distributed-shared-memory round trip per rank
-        float2 p0[8], p1[8];
-        float ps[8];
-#pragma unroll
-        for (int r = 0; r < 8; r++) {
-            p0[r] = p1[r] = make_float2(0.f, 0.f);
-            ps[r] = 0.f;
-            if (r < KS) {
-                const float* peer = cluster.map_shared_rank(red, r);
-                p0[r] = make_float2(peer[tok * kRedLd + c], peer[tok * kRedLd + c + 1]);
-                if (DUAL) p1[r] = make_float2(peer[(MP + tok) * kRedLd + c], peer[(MP + tok) * kRedLd + c + 1]);
-                if (!FUSED && ep.rms) ps[r] = peer[NW * MP * kRedLd + tok];
-            }
-        }
-        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
-        float ss = 0.f;
-#pragma unroll
-        for (int r = 0; r < 8; r++) {  // rank order: the sum does not depend on which block does it
-            s0.x += p0[r].x;
-            s0.y += p0[r].y;
-            s1.x += p1[r].x;
-            s1.y += p1[r].y;
-            ss += ps[r];
-        }
-        if (tok < M && n0 + c < N) {  // N is even: the second column is inside too
-            if (!FUSED && ep.rms) {
-                const float inv = rsqrtf(ss / (float)K + ep.rms_eps);
-                s0.x *= inv;
-                s0.y *= inv;
-                s1.x *= inv;
-                s1.y *= inv;
-            }
-            float v0 = DUAL ? (s0.x / (1.0f + __expf(-s0.x))) * s1.x : s0.x;
-            float v1 = DUAL ? (s0.y / (1.0f + __expf(-s0.y))) * s1.y : s0.y;
-            const size_t idx = (size_t)tok * N + n0 + c;
-            if (tp) {
-                // push this rank's value of the two elements to every peer, then gather theirs
-                const __half2 own = __floats2half2_rn(v0, v1);
-                const uint32_t word = *reinterpret_cast<const uint32_t*>(&own);
-#pragma unroll
-                for (int r = 0; r < 8; r++)
-                    if (r < ep.tp.world && r != ep.tp.rank)
-                        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(ep.tp.push[r] + idx / 2), "r"(word), "r"(seq)
-                                     : "memory");
-                v0 = v1 = 0.f;
-#pragma unroll
-                for (int r = 0; r < 8; r++)
-                    if (r < ep.tp.world) {
-                        uint32_t w = word;
-                        if (r != ep.tp.rank) {
-                            const uint2* src = ep.tp.mine + (size_t)r * ep.tp.slot_words + idx / 2;
-                            uint32_t got;
-                            for (;;) {
-                                asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(w), "=r"(got) : "l"(src) : "memory");
-                                if (got == seq) break;
-                                if (clock64() - t_start > 2000LL * 1000 * 1000) {  // about a second: give up, say so, go on
-                                    atomicExch(ep.tp.error, 1);
-                                    break;
-                                }
-                            }
-                        }
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-                        v0 += f.x;
-                        v1 += f.y;
-                    }
-            }
-            if (!FUSED && ep.resid) {
-                const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(ep.resid + idx));
-                v0 += rr.x;
-                v1 += rr.y;
-                if (ep.bias) {
-                    const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(ep.bias + n0 + c));
-                    v0 += bb.x;
-                    v1 += bb.y;
-                }
-            }
-            *reinterpret_cast<__half2*>(y + idx) = __floats2half2_rn(v0, v1);
-        }
-    }
+    splitk_epilogue<MP, DUAL, FUSED, kStThreads>(red, cluster, y, M, N, K, n0, ep);
     cluster.sync();  // peers may still be reading this block's tile
 }
 
@@ -488,6 +373,14 @@ struct StagedPlan {
     cudaError_t status;  // cudaErrorInvalidConfiguration: the tensor-parallel epilogue was asked for and no plan fits one wave
 };
 
+// Plans forced from outside (onellm_gemm_plan_override): (N, K, dual) -> (K split, ring depth)
+static std::map<std::tuple<int, int, bool>, std::pair<int, int>>& plan_overrides()
+{
+    static std::map<std::tuple<int, int, bool>, std::pair<int, int>> t;
+    return t;
+}
+static std::mutex g_override_mu;
+
 template <int MB, bool DUAL, bool FUSED>
 static StagedPlan plan_staged(int N, int K, bool tp)
 {
@@ -504,14 +397,27 @@ static StagedPlan plan_staged(int N, int K, bool tp)
         return prefer_max_shared((const void*)kern);
     });
     if (plan.status != cudaSuccess) return plan;
+    const int col_blocks = (N + kBN - 1) / kBN;
+    const int total_stages = (K + kKC - 1) / kKC;
+    {
+        std::lock_guard<std::mutex> lock(g_override_mu);
+        auto ov = plan_overrides().find(std::make_tuple(N, K, DUAL));
+        if (ov != plan_overrides().end() && !tp) {
+            plan.ks = std::max(1, std::min(ov->second.first, std::min(8, total_stages)));
+            plan.nst = std::max(3, std::min(ov->second.second, 12));  // the prologue holds at most 11 stages of activations in registers
+            plan.per_block = (total_stages + plan.ks - 1) / plan.ks;
+            const size_t xn = FUSED ? (size_t)8 * MB * (plan.per_block * kKC + 8) * sizeof(__half) : 0;
+            plan.smem = std::max(stage * plan.nst, red) + xn;
+            if (plan.smem > smem_cap) plan.status = cudaErrorInvalidConfiguration;
+            return plan;
+        }
+    }
     static std::mutex mu;  // the plan and occupancy caches
     std::lock_guard<std::mutex> lock(mu);
     static std::map<std::tuple<int, int, bool, int>, StagedPlan> plans;  // one table per instantiation
     const auto key = std::make_tuple(N, K, tp, current_device());
     auto it = plans.find(key);
     if (it != plans.end()) return it->second;
-    const int col_blocks = (N + kBN - 1) / kBN;
-    const int total_stages = (K + kKC - 1) / kKC;
     // The K split (= cluster size, 1..8) and ring depth that keep the most bytes in flight
     // while every block is resident at once (residency asked from the runtime, because clusters
     // do not always pack the SMs of a GPC fully).  A sweep over (split, depth) on B200 for the
@@ -580,12 +486,46 @@ static cudaError_t launch_staged(const __half* x, const __half* W0, const __half
     return cudaLaunchKernelEx(&cfg, kern, x, W0, W1, y, M, N, K, plan.per_block, plan.nst, fn, ep);
 }
 
+template <int MB>
+static StagedPlan plan_for(bool dual, int N, int K)
+{
+    return dual ? plan_staged<MB, true, false>(N, K, false) : plan_staged<MB, false, false>(N, K, false);
+}
+
+// The plan a projection of M tokens would be launched with (K split, ring depth, thread blocks).
+cudaError_t staged_plan_query(int M, int N, int K, bool dual, int* ks, int* nst, int* blocks)
+{
+    const StagedPlan p = M <= 8 ? plan_for<1>(dual, N, K) : M <= 16 ? plan_for<2>(dual, N, K) : M <= 32 ? plan_for<4>(dual, N, K) : plan_for<8>(dual, N, K);
+    if (ks) *ks = p.ks;
+    if (nst) *nst = p.nst;
+    if (blocks) *blocks = p.ks * ((N + kBN - 1) / kBN);
+    return p.status;
+}
+
+void staged_plan_override(int N, int K, bool dual, int ks, int nst)
+{
+    std::lock_guard<std::mutex> lock(g_override_mu);
+    if (ks <= 0)
+        plan_overrides().erase(std::make_tuple(N, K, dual));
+    else
+        plan_overrides()[std::make_tuple(N, K, dual)] = std::make_pair(ks, nst);
+}
+
+// skinny_gemm_tc.cu
+bool skinny_tc_takes(int M, int N, int K);
+cudaError_t skinny_tc_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K, const EpilogueArgs& ep,
+                               cudaStream_t st);
+
 // One pass of at most 64 tokens.  Called from skinny_gemm.cu.
 cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N,
                                       int K, bool dual, cudaStream_t st, const __half* resid, const __half* bias,
                                       float rms_eps, const TpEpilogue* tp)
 {
     const FusedNormArgs none = {nullptr, nullptr, nullptr, nullptr, 0.f};
+    if (skinny_tc_takes(M, N, K)) {  // more than a few 8-token rows: the tcgen05 kernel (skinny_gemm_tc.cu)
+        const EpilogueArgs ep_tc = {resid, resid ? bias : nullptr, rms_eps, rms_eps >= 0.f ? 1 : 0, 1, tp ? *tp : TpEpilogue{}};
+        return skinny_tc_dispatch(x, W0, dual ? W1 : nullptr, y, M, N, K, ep_tc, st);
+    }
     // the next kernel is released as soon as this one's first weight copies are out: its blocks cannot
     // become resident before blocks of this kernel retire (shared memory), but its launch latency is hidden
     const EpilogueArgs ep = {resid, resid ? bias : nullptr, rms_eps, rms_eps >= 0.f ? 1 : 0, 1, tp ? *tp : TpEpilogue{}};

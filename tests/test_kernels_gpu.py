@@ -488,3 +488,40 @@ def test_gemm_f16_tensor_core_tiles(ob, cuda, orc, M, N, K, nk):
     assert ob.lib().onellm_gemm_timeout_flag() == 0
     assert rel_err(y.float().cpu().numpy(), orc.gemm(x, W, w_is_nk=nk)) < TOL["f16"]
 
+
+
+@pytest.mark.parametrize("M", [17, 25, 64])
+@pytest.mark.parametrize("N,K,dual,rms,resid", [
+    (1920, 5120, False, True, False),     # 13B QKV, one of eight ranks: 15 column tiles, the K range split eight ways
+    (5120, 640, False, False, True),      # 13B o_proj slice: ten 64-row stages in all
+    (1728, 5120, True, True, False),      # gate/up slice: the last column tile is half empty
+    (32000, 4096, False, False, False),   # LM head: more column tiles than SMs
+    (1000, 528, True, False, True),       # ragged in N and K
+])
+def test_gemm_tensor_core_weight_streaming_kernel(ob, cuda, orc, M, N, K, dual, rms, resid):
+    """The tcgen05 kernel for 17..64 tokens (forced from 17 tokens up here) against the oracle, and bit-identical to itself."""
+    torch = cuda
+    before = ob.gemm_tc_min_tokens(17)
+    try:
+        rng = np.random.default_rng(M + N + K)
+        x = _round(2.0 * rng.standard_normal((M, K)), "f16")
+        W = _round(0.02 * rng.standard_normal((K, N)), "f16")
+        Wu = _round(0.02 * rng.standard_normal((K, N)), "f16") if dual else None
+        r = _round(rng.standard_normal((M, N)), "f16") if resid else None
+        inv = 1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5) if rms else 1.0
+        t0 = orc.gemm(x, W) * inv
+        ref = orc.swiglu2(t0.astype(np.float32), (orc.gemm(x, Wu) * inv).astype(np.float32)) if dual else t0
+        if resid:
+            ref = ref + r
+        outs = []
+        for _ in range(2):
+            y = _dev(torch, r, "f16") if resid else torch.zeros(M, N, device="cuda", dtype=torch.float16)
+            ob.gemm_fused(ob.F16, _dev(torch, x, "f16"), _dev(torch, W, "f16"), None if Wu is None else _dev(torch, Wu, "f16"), y, M, N, K,
+                          rms_eps=1e-5 if rms else -1.0, resid=y if resid else None, bias=None)
+            outs.append(y)
+        torch.cuda.synchronize()
+        assert ob.lib().onellm_gemm_timeout_flag() == 0
+        assert rel_err(outs[0].float().cpu().numpy(), ref) < TOL["f16"]
+        assert torch.equal(outs[0], outs[1])
+    finally:
+        ob.gemm_tc_min_tokens(before)
