@@ -420,6 +420,17 @@ typedef struct onellm_llama_config {
 } onellm_llama_config;
 
 ONELLM_API int onellm_llama_create(const onellm_llama_config* cfg, onellm_llama** out);
+/* The configuration from the config.ini the reference's converter writes next to the weight files
+ * (tools/FT_convert_weight_to_bin_final.py:43-64, section [llama]: head_num, kv_head_num, hidden_size, head_size,
+ * inter_size, num_layer, vocab_size, bos_token_id, eos_token_id, weight_data_type, max_position_embeddings,
+ * rope_theta, rms_norm_eps, attention_bias, top_k).  onellm_llama_config_from_ini fills the fields the file names
+ * and leaves max_batch, tp_rank and tp_size as the caller set them (max_seq_len too unless it is <= 0, in which
+ * case it becomes max_position_embeddings); *top_k (may be NULL) receives the file's top_k.  No GPU is touched.
+ * onellm_llama_create_from_ini does that, creates the model and sets its sampling to the file's top_k.
+ * Missing file, section or required key, or a malformed value: ONELLM_ERR_IO with the key in the message. */
+ONELLM_API int onellm_llama_config_from_ini(const char* path, onellm_llama_config* cfg, int* top_k);
+ONELLM_API int onellm_llama_create_from_ini(const char* path, int max_batch, int max_seq_len, int tp_rank, int tp_size,
+                                            onellm_llama** out);
 ONELLM_API void onellm_llama_destroy(onellm_llama* m);
 ONELLM_API size_t onellm_llama_device_bytes(const onellm_llama* m);
 ONELLM_API void* onellm_llama_stream(onellm_llama* m);

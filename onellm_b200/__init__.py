@@ -296,8 +296,27 @@ def nccl_unique_id() -> bytes:
     return buf.raw
 
 
+def llama_config_from_ini(path, max_batch=1, max_seq_len=0, tp_rank=0, tp_size=1):
+    """(LlamaConfig, top_k) from the reference converter's config.ini; touches no GPU."""
+    cfg = LlamaConfig()
+    cfg.max_batch, cfg.max_seq_len, cfg.tp_rank, cfg.tp_size, cfg.bos_id, cfg.eos_id = max_batch, max_seq_len, tp_rank, tp_size, 1, 2
+    top_k = C.c_int(0)
+    _check(lib().onellm_llama_config_from_ini(str(path).encode(), C.byref(cfg), C.byref(top_k)))
+    return cfg, top_k.value
+
+
 class Llama:
     """Host-side handle of the C++ model (weights, KV cache, generation loop)."""
+
+    @classmethod
+    def from_ini(cls, path, max_batch, max_seq_len, tp_rank=0, tp_size=1):
+        """The model described by the reference converter's config.ini (sampling set to the file's top_k)."""
+        self = cls.__new__(cls)
+        self.cfg, _ = llama_config_from_ini(path, max_batch, max_seq_len, tp_rank, tp_size)
+        self._h = C.c_void_p(0)
+        _check(lib().onellm_llama_create_from_ini(str(path).encode(), C.c_int(max_batch), C.c_int(max_seq_len), C.c_int(tp_rank),
+                                                  C.c_int(tp_size), C.byref(self._h)))
+        return self
 
     def __init__(self, *, num_layers, hidden, head_num, kv_head_num, head_size, inter_size, vocab_size,
                  max_seq_len, max_batch, rope_base=10000.0, rot_dim=0, rms_eps=1e-5, bos_id=1, eos_id=2,

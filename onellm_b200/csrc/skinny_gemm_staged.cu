@@ -373,6 +373,23 @@ struct StagedPlan {
     cudaError_t status;  // cudaErrorInvalidConfiguration: the tensor-parallel epilogue was asked for and no plan fits one wave
 };
 
+// Launch plans found by sweeping (K split, ring depth) with the decoder layer's five kernels as one CUDA graph as the
+// objective (batch 8, B200): the Llama-2-7B projections whole and sliced 2, 4 and 8 ways.  The general rule below
+// (most bytes in flight with every block resident) is within a few percent on the whole shapes but picks too few,
+// too deep blocks for the narrow slices (the 2-way gate/up slice: 129 blocks of 12 stages, 21 us; 215 blocks of
+// 4 stages, 10 us less for the layer).
+struct TunedPlan {
+    int N, K;
+    bool dual;
+    int ks, nst;
+};
+static const TunedPlan kTunedPlans[] = {
+    {12288, 4096, false, 5, 5}, {4096, 4096, false, 8, 8},  {11008, 4096, true, 3, 6}, {4096, 11008, false, 8, 10},
+    {6144, 4096, false, 8, 6},  {4096, 2048, false, 6, 5},  {5504, 4096, true, 5, 4},  {4096, 5504, false, 8, 10},
+    {3072, 4096, false, 8, 10}, {4096, 1024, false, 6, 4},  {2752, 4096, true, 8, 5},  {4096, 2752, false, 8, 8},
+    {1536, 4096, false, 8, 4},  {4096, 512, false, 4, 4},   {1376, 4096, true, 8, 5},  {4096, 1376, false, 8, 4},
+};
+
 // Plans forced from outside (onellm_gemm_plan_override): (N, K, dual) -> (K split, ring depth)
 static std::map<std::tuple<int, int, bool>, std::pair<int, int>>& plan_overrides()
 {
@@ -418,6 +435,24 @@ static StagedPlan plan_staged(int N, int K, bool tp)
     const auto key = std::make_tuple(N, K, tp, current_device());
     auto it = plans.find(key);
     if (it != plans.end()) return it->second;
+    // Shapes that were swept on B200 (python -m onellm_b200.tune_plans) take the plan that made the whole decoder layer
+    // fastest, as long as its blocks are all resident at once on this device.
+    if (MB == 1 && !FUSED) {
+        for (const TunedPlan& t : kTunedPlans) {
+            if (t.N != N || t.K != K || t.dual != DUAL || t.ks > total_stages) continue;
+            const int per = (total_stages + t.ks - 1) / t.ks;
+            const size_t smem = std::max(stage * t.nst, red);
+            if (smem > smem_cap || per * (t.ks - 1) >= total_stages) break;
+            if (staged_slots(kern, t.ks, t.nst, smem, col_blocks) < (long)col_blocks * t.ks) break;
+            if (tp && (long)col_blocks * t.ks > kTpMaxBlocks) break;
+            plan.ks = t.ks;
+            plan.nst = t.nst;
+            plan.per_block = per;
+            plan.smem = smem;
+            plans[key] = plan;
+            return plan;
+        }
+    }
     // The K split (= cluster size, 1..8) and ring depth that keep the most bytes in flight
     // while every block is resident at once (residency asked from the runtime, because clusters
     // do not always pack the SMs of a GPC fully).  A sweep over (split, depth) on B200 for the

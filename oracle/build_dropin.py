@@ -5,7 +5,7 @@ against the drop-in headers of this repository (include/onellm) and links them w
 
 Test infrastructure only: it shows that a oneLLM tree builds on top of this library without edits, and
 produces the programs the GPU tests run (the reference's unit tests on this library's kernels, and
-tests/cpp/dropin_layers.cpp, which drives the reference's layer classes).  No reference source is copied
+tests/cpp/dropin_*.cpp, which drive the reference's layer classes).  No reference source is copied
 and the reference's build system is not used.  Outputs go to oracle/_ref/dropin/ only (git-ignored).
 Include order: include/onellm first, so "src/utils/..", "src/kernels/..", "src/weights/..",
 "src/memory/.." and "src/models/.." resolve to the drop-in headers; the reference tree second, for the
@@ -28,6 +28,10 @@ EXAMPLES = {"ffn_example": ("examples/cpp/ffn/ffn_example.cpp", ["ffn"]),
             "context_attn_example": ("examples/cpp/attention/context_attn_example.cpp", ["context_attention"]),
             "self_decoder_example": ("examples/cpp/decoder/self_decoder_example.cpp", ["self_decoder", "masked_self_attention", "ffn"]),
             "context_decoder_example": ("examples/cpp/decoder/context_decoder_example.cpp", ["context_decoder", "context_attention", "ffn"])}
+# this repository's programs that drive the layer classes (tests/cpp) -> layer objects they link
+DRIVERS = {"dropin_layers": ["context_attention", "masked_self_attention"],
+           "dropin_self_decoder": ["self_decoder", "masked_self_attention", "ffn"],
+           "dropin_context_decoder": ["context_decoder", "context_attention", "ffn"]}
 # unit tests that build; test_decoder_masked_attn.cu and the empty test_layernorm.cu do not build in the
 # reference tree either
 UNIT_TESTS = ["test_activation", "test_append_kvcache", "test_batch_gemm", "test_beamsearch_topK", "test_cal_paddingoffset",
@@ -63,17 +67,18 @@ def build(ref):
     # the unit tests use CUDA's host-side rsqrt/min: nvcc, although they hold no device code
     nvcc = ["nvcc", "-std=c++17", "-w", "-gencode", "arch=compute_100a,code=sm_100a"] + inc
     jobs += [(t, nvcc + ["-c", os.path.join(ref, "tests", "unittests", t + ".cu"), "-o", obj(t)]) for t in UNIT_TESTS]
-    jobs.append(("dropin_layers", cxx + ["-c", os.path.join(ROOT, "tests", "cpp", "dropin_layers.cpp"), "-o", obj("dropin_layers")]))
+    jobs += [(n, cxx + ["-I" + os.path.join(ROOT, "tests", "cpp"), "-c", os.path.join(ROOT, "tests", "cpp", n + ".cpp"), "-o", obj(n)])
+             for n in DRIVERS]
     _run(jobs)
     link = ["-L" + os.path.join(ROOT, "onellm_b200"), "-lonellm_b200", "-L" + os.path.join(cuda, "lib64"), "-lcudart", "-lcublas",
             "-Wl,-rpath,$ORIGIN/../../../onellm_b200"]
     jobs = [(n, [gxx, "-o", os.path.join(OUT, n), obj(n)] + [obj(d) for d in deps] + link) for n, (_, deps) in EXAMPLES.items()]
     jobs += [(t, [gxx, "-o", os.path.join(OUT, t), obj(t)] + link) for t in UNIT_TESTS]
-    jobs.append(("dropin_layers", [gxx, "-o", os.path.join(OUT, "dropin_layers"), obj("dropin_layers"), obj("context_attention"),
-                                   obj("masked_self_attention")] + link))
+    jobs += [(n, [gxx, "-o", os.path.join(OUT, n), obj(n)] + [obj(d) for d in deps] + link) for n, deps in DRIVERS.items()]
     _run(jobs)
     return OUT
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    default = os.environ.get("ONELLM_REFERENCE_TREE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else default))

@@ -53,4 +53,5 @@ def build(ref):
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    default = os.environ.get("ONELLM_REFERENCE_TREE", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else default))

@@ -1,7 +1,9 @@
-// Drives the reference's own layer classes (LLaMAContextAttentionLayer, LLaMASelfAttentionLayer, compiled
+// Drives the reference's own attention layer classes (LLaMAContextAttentionLayer, LLaMASelfAttentionLayer, compiled
 // unchanged from the oneLLM tree) and the launch* entry points through the drop-in headers, on seeded
 // inputs, and writes every result as a raw float file into the directory given as argv[1].  The pytest
-// side regenerates the same inputs and checks the files against the CPU oracle.
+// side regenerates the same inputs and checks the files against the CPU oracle.  (The FFN layer and the two
+// decoder classes are driven by dropin_self_decoder.cpp and dropin_context_decoder.cpp: the reference's layer
+// headers carry no include guards, so the two decoders cannot share a translation unit.)
 #include <cstdint>
 #include <cstdio>
 #include <string>
@@ -20,38 +22,7 @@
 #include "src/memory/allocator/cuda_allocator.h"
 #include "src/weights/llama/llama_weights.h"
 
-static uint32_t g_state = 12345u;
-static float next_uniform()  // the generator tests/test_dropin_gpu.py mirrors
-{
-    g_state = g_state * 1664525u + 1013904223u;
-    return (float)(g_state >> 8) / 16777216.0f - 0.5f;
-}
-static std::vector<float> randv(size_t n, float scale)
-{
-    std::vector<float> v(n);
-    for (auto& x : v) x = next_uniform() * scale;
-    return v;
-}
-template <typename T>
-static T* to_dev(const std::vector<T>& h)
-{
-    T* d = nullptr;
-    CHECK(cudaMalloc((void**)&d, h.size() * sizeof(T)));
-    CHECK(cudaMemcpy(d, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice));
-    return d;
-}
-static std::string g_dir;
-static void dump(const char* name, const void* dev, size_t n_floats)
-{
-    std::vector<float> h(n_floats);
-    CHECK(cudaMemcpy(h.data(), dev, n_floats * sizeof(float), cudaMemcpyDeviceToHost));
-    std::FILE* f = std::fopen((g_dir + "/" + name + ".f32").c_str(), "wb");
-    if (!f || std::fwrite(h.data(), sizeof(float), n_floats, f) != n_floats) {
-        std::fprintf(stderr, "cannot write %s\n", name);
-        std::exit(2);
-    }
-    std::fclose(f);
-}
+#include "dropin_common.h"
 
 int main(int argc, char** argv)
 {

@@ -7,7 +7,8 @@ import sys
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE_TREE = "/root/reference"
+# the oneLLM source tree: ONELLM_REFERENCE_TREE, or a directory named "reference" beside this repository
+REFERENCE_TREE = os.environ.get("ONELLM_REFERENCE_TREE", os.path.join(os.path.dirname(ROOT), "reference"))
 GXX = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
 
 HEADERS = """
@@ -71,6 +72,6 @@ def test_reference_layers_examples_and_unit_tests_build_unchanged(ob):
     finally:
         sys.path.pop(0)
     out = build_dropin.build(REFERENCE_TREE)
-    for name in list(build_dropin.EXAMPLES) + build_dropin.UNIT_TESTS + ["dropin_layers"]:
+    for name in list(build_dropin.EXAMPLES) + build_dropin.UNIT_TESTS + list(build_dropin.DRIVERS):
         assert os.access(os.path.join(out, name), os.X_OK), name
     assert set(build_dropin.RUNNABLE) <= set(build_dropin.UNIT_TESTS)

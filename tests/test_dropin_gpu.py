@@ -1,5 +1,5 @@
 """The reference's own code on this library's kernels: (1) its layer classes, compiled unchanged against
-the drop-in headers and driven by tests/cpp/dropin_layers.cpp, against the CPU oracle; (2) its unit-test
+the drop-in headers and driven by tests/cpp/dropin_*.cpp, against the CPU oracle; (2) its unit-test
 programs, unchanged, whose own CPU checks must agree.  The programs are prebuilt by
 oracle/build_dropin.py where a oneLLM tree is present."""
 import os
@@ -162,3 +162,88 @@ def test_reference_unit_test_activation():
     out = _run("test_activation")
     m = re.search(r"the (\d+)th res is wrong", out)
     assert "test passed" in out or (m and int(m.group(1)) < 32), out[-500:]
+
+
+def _layer_weights(g, hidden, QH, D, inter):
+    """The draws of the decoder drivers (tests/cpp/dropin_*_decoder.cpp), in their order."""
+    w = {"g_attn": g.randv(hidden, 1.0), "g_ffn": g.randv(hidden, 1.0),
+         "Wqkv": g.randv(hidden * QH * D, 0.2).reshape(hidden, QH * D), "bqkv": g.randv(QH * D, 0.2),
+         "Wo": g.randv(hidden * hidden, 0.2).reshape(hidden, hidden), "bo": g.randv(hidden, 0.2)}
+    for k in ("Wg", "Wu"):
+        w[k] = g.randv(hidden * inter, 0.2).reshape(hidden, inter)
+    w["Wd"] = g.randv(inter * hidden, 0.2).reshape(inter, hidden)
+    w["g_out"] = g.randv(hidden, 1.0)
+    return w
+
+
+def _decoder_tail(orc, xn, attn, w):
+    """What both decoder classes do behind the attention of a layer (self_decoder.cpp:50-73, context_decoder.cpp:104-128):
+    add-residual RMSNorm with the attention's output bias, the FFN (whose result never leaves the layer: ffn.cpp:59-72
+    writes a buffer of its own), add-residual RMSNorm with the next gamma."""
+    normed1, res1 = orc.add_residual_rmsnorm(xn, attn, w["bo"], w["g_ffn"], 1e-5)
+    normed2, res2 = orc.add_residual_rmsnorm(res1, normed1, None, w["g_out"], 1e-5)
+    return normed2, res2
+
+
+@needs_programs
+def test_reference_ffn_layer_and_context_decoder_on_these_kernels(orc, tmp_path):
+    p = subprocess.run([os.path.join(BIN, "dropin_context_decoder"), str(tmp_path)], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "dropin_context_decoder ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+    B, H, Hkv, D, S, inter = 2, 4, 2, 32, 24, 192
+    hidden, QH = H * D, H + 2 * Hkv
+    g = Lcg()
+    # LLaMAFFNLayer::forward: the down projection in the layer's own buffer
+    T = 3
+    X = g.randv(T * hidden, 2.0).reshape(T, hidden)
+    Wg = g.randv(hidden * inter, 0.2).reshape(hidden, inter)
+    Wu = g.randv(hidden * inter, 0.2).reshape(hidden, inter)
+    Wd = g.randv(inter * hidden, 0.2).reshape(inter, hidden)
+    want = orc.gemm(orc.swiglu2(orc.gemm(X, Wg), orc.gemm(X, Wu)), Wd)
+    assert rel_err(_load(tmp_path, "ffn_class_down_out", (T, hidden)), want) < 2e-5
+    # LlamaContextDecoder::forward, one layer
+    w = _layer_weights(g, hidden, QH, D, inter)
+    lens, hist, ctx, T, max_q, max_k = [5, 3], [2, 0], [7, 3], 8, 5, 7
+    X = g.randv(T * hidden, 2.0).reshape(T, hidden)
+    kc = g.randv(B * Hkv * S * D, 2.0).reshape(B, Hkv, S, D)
+    vc = g.randv(B * Hkv * S * D, 2.0).reshape(B, Hkv, S, D)
+    xn = orc.rmsnorm(X, w["g_attn"], 1e-5)
+    po, cum, n = orc.cal_padding_offset(lens, max_q)
+    mask = orc.build_causal_mask(lens, ctx, max_q, max_k, attend_history=False)
+    qkv = orc.gemm(xn, w["Wqkv"]).reshape(T, QH, D)
+    q_r, k_r, v_r = orc.qkv_bias_rope_transpose(qkv, w["bqkv"], po, hist, B, max_q, H, Hkv, D, 10000.0)
+    orc.append_kv_cache(kc, k_r, lens, hist)
+    orc.append_kv_cache(vc, v_r, lens, hist)
+    k_rep, v_rep = orc.repeat_kv(kc, ctx, H, max_k), orc.repeat_kv(vc, ctx, H, max_k)
+    qk = np.einsum("bhqd,bhkd->bhqk", q_r.astype(np.float64), k_rep.astype(np.float64)).astype(np.float32)
+    prob = orc.scale_mask_softmax(qk, mask, D ** -0.5)
+    pv = np.einsum("bhqk,bhkd->bhqd", prob.astype(np.float64), v_rep.astype(np.float64)).astype(np.float32)
+    attn = orc.gemm(orc.transpose_remove_padding(pv, po, T).reshape(T, hidden), w["Wo"])
+    out, res = _decoder_tail(orc, xn, attn, w)
+    assert rel_err(_load(tmp_path, "cdec_k_cache", kc.shape), kc) < 1e-5
+    assert rel_err(_load(tmp_path, "cdec_v_cache", vc.shape), vc) < 1e-5
+    assert rel_err(_load(tmp_path, "cdec_residual", (T, hidden)), res) < 5e-5
+    assert rel_err(_load(tmp_path, "cdec_out", (T, hidden)), out) < 5e-5
+
+
+@needs_programs
+def test_reference_self_decoder_on_these_kernels(orc, tmp_path):
+    p = subprocess.run([os.path.join(BIN, "dropin_self_decoder"), str(tmp_path)], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "dropin_self_decoder ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+    B, H, Hkv, D, S, inter, step = 2, 4, 2, 32, 24, 192, 4
+    hidden, QH = H * D, H + 2 * Hkv
+    g = Lcg()
+    w = _layer_weights(g, hidden, QH, D, inter)
+    X = g.randv(B * hidden, 2.0).reshape(B, hidden)
+    kc = g.randv(B * Hkv * S * D, 2.0).reshape(B, Hkv, S, D)
+    vc = g.randv(B * Hkv * S * D, 2.0).reshape(B, Hkv, S, D)
+    xn = orc.rmsnorm(X, w["g_attn"], 1e-5)
+    qkv = orc.gemm(xn, w["Wqkv"]).reshape(B, QH, D)
+    b = w["bqkv"]
+    o = orc.decode_attn(qkv[:, :H], qkv[:, H:H + Hkv], qkv[:, H + Hkv:], kc, vc, step, rope_pos=step, rot_dim=D,
+                        bias_q=b[:H * D], bias_k=b[H * D:(H + Hkv) * D], bias_v=b[(H + Hkv) * D:])
+    attn = orc.gemm(o.reshape(B, hidden), w["Wo"])
+    out, res = _decoder_tail(orc, xn, attn, w)
+    assert rel_err(_load(tmp_path, "sdec_k_cache", kc.shape), kc) < 1e-5
+    assert rel_err(_load(tmp_path, "sdec_v_cache", vc.shape), vc) < 1e-5
+    assert rel_err(_load(tmp_path, "sdec_residual", (B, hidden)), res) < 5e-5
+    assert rel_err(_load(tmp_path, "sdec_out", (B, hidden)), out) < 5e-5

@@ -207,3 +207,23 @@ def test_ragged_turn_after_ragged_prompts(ob, cuda, orc, tmp_path):
     with pytest.raises(ob.OnellmError):
         m.prefill_ragged([np.zeros(200, np.int32), np.zeros(3, np.int32)])  # longer than max_seq_len
     m.close()
+
+
+def test_model_from_the_converters_config_ini(ob, cuda, tmp_path):
+    """onellm_llama_create_from_ini: the model described by a config.ini as the reference's converter writes it."""
+    import configparser
+    cp = configparser.ConfigParser()
+    cp["llama"] = {"model_name": "toy", "head_num": "4", "kv_head_num": "2", "hidden_size": "256", "head_size": "64",
+                   "inter_size": "512", "num_layer": "2", "vocab_size": "1000", "bos_token_id": "1", "eos_token_id": "2",
+                   "weight_data_type": "fp16", "max_position_embeddings": "4096", "rope_theta": "10000.0",
+                   "rms_norm_eps": "1e-05", "attention_bias": "False", "top_k": "7"}
+    path = os.path.join(str(tmp_path), "config.ini")
+    with open(path, "w") as f:
+        cp.write(f)
+    m = ob.Llama.from_ini(path, max_batch=2, max_seq_len=64)
+    assert (m.cfg.num_layers, m.cfg.kv_head_num, m.cfg.vocab_size, m.cfg.max_seq_len) == (2, 2, 1000, 64)
+    m.init_random(seed=5)
+    a = m.generate(np.zeros((2, 3), np.int32), 5)       # sampling with the file's top_k = 7, seeded by the step
+    b = m.generate(np.zeros((2, 3), np.int32), 5)
+    assert a.shape == (2, 5) and np.array_equal(a, b) and a.min() >= 0 and a.max() < 1000
+    m.close()
