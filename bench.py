@@ -441,7 +441,20 @@ def run_ours(args, workload):
         check["rel_err_logits"] = float(np.max(np.abs(lg_a - lg_b)) / scale)
         check["ids_equal"] = bool(np.array_equal(np.argmax(lg_a, axis=2), np.argmax(lg_b, axis=2)))
         check["compared"] = ("logits of 4 decode steps from the same cache state and input ids: exchange over peer memory "
-                             "vs ncclAllReduce; ids = their argmax")
+                             "vs ncclAllReduce; ids = their argmax.  The two are different fp16 pipelines (the peer-memory "
+                             "step sums the ranks' partials and the residual in fp32 and has no norm kernel; the NCCL step "
+                             "rounds the partials, their fp16 sum and the normalised activations): they agree to rounding "
+                             "accumulated over all layers, about 1e-2 of the largest logit at 32-40 layers, while a wrong "
+                             "exchange gives errors of order 1; the run fails above 3e-2")
+    if world > 1:
+        # every rank must hold bit-identical logits (the peer-memory sums are taken in rank order on every rank)
+        bits = np.ascontiguousarray(lg_a.astype(np.float16)).view(np.uint16).astype(np.int64).ravel()
+        sig = torch.tensor([int(bits.sum()), int((bits * (np.arange(bits.size, dtype=np.int64) % 8191 + 1)).sum())], device="cuda",
+                           dtype=torch.int64)
+        lo, hi = sig.clone(), sig.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        check["ranks_bit_identical"] = bool(torch.equal(lo, hi))
     m.set_sampling(top_k=1, temperature=1.0)
     m.seek(batch, prompt_len, first)
     greedy = np.zeros(batch, np.int32)
@@ -456,7 +469,7 @@ def run_ours(args, workload):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         check["p2p_error"], check["tc_timeout_flag"] = int(t[0].item()), int(t[1].item())
     failed = (check["p2p_error"] != 0 or check["tc_timeout_flag"] != 0 or not check["logits_finite"]
-              or check.get("rel_err_logits", 0.0) > 3e-3)
+              or check.get("rel_err_logits", 0.0) > 3e-2 or not check.get("ranks_bit_identical", True))
 
     hbm_peak, tf_peak, peak_kind = peaks()
     line = None
