@@ -302,8 +302,9 @@ def config_cases(torch, hbm_peak, tf_peak):
     t = kc.time_case(case, torch, iters=10, warm=3)
     out["prefill_layer_f16_t1024"] = {"launches": case.launches, "flops_dense": case.amount, "ms": t * 1e3,
                                       "tflops": case.amount / t / 1e12, "frac_of_tensor_peak": case.amount / t / 1e12 / tf_peak,
-                                      "note": "QKV, RoPE + cache write, causal attention, o_proj, add-residual RMSNorm, gate/up + "
-                                              "SwiGLU, down, add-residual RMSNorm; attention counted over the full square"}
+                                      "note": "one decoder layer of the context phase as the model runs it on one GPU: QKV (RMS scale in "
+                                              "the epilogue), RoPE + cache write, causal attention, o_proj + residual, gate/up + SwiGLU, "
+                                              "down + residual; attention counted over the full square"}
     del case
     torch.cuda.empty_cache()
     return out

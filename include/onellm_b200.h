@@ -66,7 +66,12 @@ ONELLM_API int onellm_abi_version(void);
  *   step_dev: optional DEVICE int.  When non-NULL the kernel reads the step from it at run
  *     time (so a captured CUDA graph can be replayed as the sequence grows); `step` must
  *     then be an upper bound of that value, and the position used is
- *     *step_dev + (rope_pos - step).
+ *     *step_dev + (rope_pos - step).  The kernel reads the counter as soon as its blocks start,
+ *     which under programmatic dependent launch can be while the kernel enqueued just before it
+ *     is still running: the counter must have been written by work that was COMPLETE before that
+ *     preceding kernel began (the model advances it in the first kernel of a step, launched with a
+ *     full stream dependency).  A counter updated by the kernel directly in front of this call
+ *     may be read at its old value.
  *   rot_dim, rope_base: rotary dimension and base, pairs (2i, 2i+1), angle
  *     rope_pos / rope_base^(2i/rot_dim).
  *   out [B,H,D] with batch stride out_stride_b.
@@ -186,6 +191,21 @@ ONELLM_API int onellm_gemm_ld(int dtype, const void* x, const void* W, void* y, 
 
 /* 1 if a block of the tensor-core GEMM gave up a bounded wait since the last call (the flag is cleared),
  * 0 otherwise, -1 if it cannot be read.  Such a block skips its stores: the output is then incomplete. */
+/* Context-phase form of onellm_gemm_fused (any M; tcgen05 tiles): a decoder layer without norm kernels over
+ * all prompt tokens at once, replacing launchLinearGemm + launchFusedAddBiasResidualRMSNorm of
+ * src/layers/decoder/context_decoder.cpp:95-131 once the norm's gamma is multiplied into the weight rows.
+ *   row_ss [M, ss_parts] (or NULL): partial sums whose total is the sum of squares of row m of x; the result
+ *     rows are scaled by rsqrt(total / K + rms_eps), i.e. the projection of RMSNorm(x).
+ *   resid [M, N] (or NULL, may be y): y = resid + bias + result.  Wu: the gate/up form, y = silu(x.W) * (x.Wu).
+ *   row_ss_out [M, onellm_gemm_rows_parts(N, 0)] (or NULL): per column tile, the sum of squares of the values
+ *     stored in y -- the row_ss of the projection that reads y next; every entry is written exactly once.
+ * onellm_row_sumsq: out[m] = sum of squares of row m (the row_ss, with one part, of a tensor that no projection
+ * produced, e.g. the embedding output). */
+ONELLM_API int onellm_gemm_rows(int dtype, const void* x, const void* W, const void* Wu, void* y, int M, int N, int K,
+                                const float* row_ss, int ss_parts, float rms_eps, const void* resid, const void* bias,
+                                float* row_ss_out, void* stream);
+ONELLM_API int onellm_gemm_rows_parts(int N, int dual);
+ONELLM_API int onellm_row_sumsq(int dtype, const void* x, int rows, int cols, float* out, void* stream);
 ONELLM_API int onellm_gemm_timeout_flag(void);
 
 /* Tuning aids for the weight-streaming projections (at most 64 tokens, [K, N] weights; no counterpart in the
@@ -358,7 +378,8 @@ ONELLM_API int onellm_topk(int dtype, const void* logits, int rows, int vocab, i
  * topk_val is NOT modified (the reference overwrites it with the weights).
  * seqlen / finished (bool bytes) may be NULL.  u_out (float [B], may be NULL) receives the
  * uniform draws.  rng_step_dev: optional DEVICE int read at run time in place of rng_step
- * (for replay inside a captured CUDA graph).
+ * (for replay inside a captured CUDA graph); like step_dev of onellm_decode_attn it is read when
+ * the kernel starts, so it must not be written by the kernel enqueued directly before this call.
  * ------------------------------------------------------------------------------------- */
 ONELLM_API int onellm_topk_sample(const int* topk_id, const float* topk_val, int B, int K,
                                   float temperature, int rng_step, const int* rng_step_dev,
@@ -464,7 +485,8 @@ ONELLM_API int onellm_llama_p2p_error(onellm_llama* m);
  * (the benchmark's result check) run the same steps both ways.  Every rank must choose the same. */
 ONELLM_API int onellm_llama_set_tp_exchange(onellm_llama* m, int peer_memory);
 /* 1: run the context phase one position at a time through the decode kernels (cross-check path);
- * 0 (default): all prompt tokens at once through the context-phase kernels. */
+ * 0 (default): all prompt tokens at once through the context-phase kernels; 2: the same with the norm kernels
+ * kept between the projections on one GPU too (what tensor-parallel runs always do; comparison). */
 ONELLM_API int onellm_llama_set_prefill_by_decode(onellm_llama* m, int enabled);
 
 /* Context phase for `batch` prompts of equal length (host ids [batch, prompt_len]); resets the

@@ -166,6 +166,19 @@ def gemm_tc_min_tokens(min_tokens=0):
     return int(lib().onellm_gemm_tc_min_tokens(C.c_int(min_tokens)))
 
 
+def gemm_rows(dtype, x, W, Wu, y, M, N, K, row_ss=None, ss_parts=0, rms_eps=1e-5, resid=None, bias=None, row_ss_out=None, stream=None):
+    _check(lib().onellm_gemm_rows(C.c_int(dtype), _p(x), _p(W), _p(Wu), _p(y), C.c_int(M), C.c_int(N), C.c_int(K), _p(row_ss),
+                                  C.c_int(ss_parts), C.c_float(rms_eps), _p(resid), _p(bias), _p(row_ss_out), _stream(stream)))
+
+
+def gemm_rows_parts(N, dual=False):
+    return int(lib().onellm_gemm_rows_parts(C.c_int(N), C.c_int(1 if dual else 0)))
+
+
+def row_sumsq(dtype, x, rows, cols, out, stream=None):
+    _check(lib().onellm_row_sumsq(C.c_int(dtype), _p(x), C.c_int(rows), C.c_int(cols), _p(out), _stream(stream)))
+
+
 def swiglu(dtype, inp, out, tokens, inter, stream=None):
     _check(lib().onellm_swiglu(C.c_int(dtype), _p(inp), _p(out), C.c_int(tokens), C.c_int(inter),
                                _stream(stream)))
@@ -378,8 +391,9 @@ class Llama:
     def set_graphs(self, enabled: bool):
         _check(lib().onellm_llama_set_graphs(self._h, C.c_int(1 if enabled else 0)))
 
-    def set_prefill_by_decode(self, enabled: bool):
-        _check(lib().onellm_llama_set_prefill_by_decode(self._h, C.c_int(1 if enabled else 0)))
+    def set_prefill_by_decode(self, enabled):
+        """False / 0: context-phase kernels; True / 1: position by position; 2: context-phase kernels with norm kernels."""
+        _check(lib().onellm_llama_set_prefill_by_decode(self._h, C.c_int(int(enabled))))
 
     def prefill(self, ids):
         """ids: int32 numpy [batch, prompt_len]; returns the first sampled id per sequence."""

@@ -25,7 +25,7 @@ struct RopeDenoms {
 __global__ void padding_offset_kernel(int* __restrict__ padding_offset, int* __restrict__ cum_seqlens,
                                       const int* __restrict__ seq_lens, int B, int max_q_len, int* __restrict__ token_num)
 {
-    // one warp: lane b owns sequence b (+32, ...); exclusive prefix sums by shuffles
+    // thread 0 takes the exclusive prefix sums of the (at most 64) lengths; the block then writes the offsets
     __shared__ int cum[65];
     if (threadIdx.x == 0) {
         int total = 0;

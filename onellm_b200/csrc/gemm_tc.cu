@@ -4,13 +4,13 @@
 // src/kernels/cublas_wrapper.cc:45-90 of the reference) for prefill shapes: y[M,N] = x[M,K] . W with
 // W [K,N] (the layer weights, N contiguous) or W [N,K] (the LM head), fp16 in, fp32 accumulate.
 //
-// One 128 x 256 output tile per block (with 128 x 128 tiles the operand traffic from L2 into shared
-// memory, 15.6 KB per MFLOP, was what bounded the kernel; the wider tile needs 11.7).  A producer
-// thread streams 64-deep K slices of both operands into a ring of four shared-memory stages with TMA
-// (cp.async.bulk.tensor, 128-byte swizzle; no cluster multicast anywhere); an MMA thread issues
-// tcgen05.mma (M = 128, N = 256, K = 16, kind::f16) with the accumulator in tensor memory (256 columns)
-// and releases each stage with tcgen05.commit; after the last slice all four warps read the
-// accumulator with tcgen05.ld, convert and store.
+// Persistent: one block per SM walks 128 x 256 output tiles (with 128 x 128 tiles the operand traffic from L2
+// into shared memory, 15.6 KB per MFLOP, was what bounded the kernel; the wider tile needs 11.7) in an order
+// that keeps the tiles in flight on a near-square patch of the output.  Warp 0 streams 64-deep K slices of
+// both operands into a ring of four shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte swizzle; no
+// cluster multicast anywhere); one thread of warp 1 issues tcgen05.mma (M = 128, N = 256, K = 16, kind::f16)
+// and releases each stage with tcgen05.commit; tensor memory holds two 256-column accumulators, so warps 2-5
+// (tcgen05.ld, convert, store) drain tile i while the MMAs of tile i + 1 run.
 // The [K,N] weight is used as it lies in memory: it is the "MN-major" B operand of the MMA
 // (four 64-column TMA boxes per stage), so no transposed copy of the weights is ever made.
 // Every wait on an mbarrier is bounded; on a time-out the block records it in a device flag,
@@ -43,10 +43,27 @@ constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + 1024 /* alignment slack
 // MODE 2: two [K,N] weights; the 256 accumulator columns of a tile are 128 columns of x.W (gate) beside the
 // same 128 columns of x.W2 (up), and the epilogue stores silu(gate) * up: the gate GEMM, the up GEMM and
 // launchAct of src/layers/ffn/ffn.cpp:62-66 in one pass, without the [T, 2, I] buffer.
+// Epilogue options that let the context phase run without norm kernels, as the decode step does (the norm's gamma
+// is multiplied into the weight rows beforehand):
+//   row_ss:  sums of squares of the rows of x, as ss_parts partial sums per row; the result rows are scaled by
+//            rsqrt(sum / K + eps), i.e. this is the projection of RMSNorm(x)
+//   resid:   y = resid + bias + result (resid may be y itself: an element is read and written by the same thread)
+//   ss_out:  [M, ceil(N / tile columns)]: the sum of squares of the stored (rounded) values of each row inside this
+//            tile's columns -- the row_ss of the projection that reads y next.  Every entry is written by exactly
+//            one block, so the sums do not depend on the order the blocks run in.
+struct TcEpilogue {
+    const float* row_ss;
+    int ss_parts;
+    float eps;
+    const __half* resid;
+    const __half* bias;
+    float* ss_out;
+};
+
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_b2, __half* __restrict__ y, int M, int N, int K)
+               const __grid_constant__ CUtensorMap map_b2, __half* y, int M, int N, int K, const TcEpilogue epi)
 {
     constexpr bool W_NK = MODE == 1;
     constexpr bool DUAL = MODE == 2;
@@ -172,6 +189,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + q * 32 + lane;
+            float inv = 1.f, sq = 0.f;
+            if (epi.row_ss && row < M) {
+                float ssum = 0.f;
+                for (int pp = 0; pp < epi.ss_parts; pp++) ssum += epi.row_ss[(size_t)row * epi.ss_parts + pp];
+                inv = rsqrtf(ssum / (float)K + epi.eps);
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < kOutN; c0 += 32) {
                 uint32_t r[32];
@@ -182,28 +205,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
-                        const float g = __uint_as_float(r[i]);
-                        r[i] = __float_as_uint(g / (1.0f + __expf(-g)) * __uint_as_float(u[i]));
+                        const float g = __uint_as_float(r[i]) * inv;
+                        r[i] = __float_as_uint(g / (1.0f + __expf(-g)) * (__uint_as_float(u[i]) * inv));
                     }
                 } else {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (epi.row_ss) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * inv);
+                    }
                 }
                 if (row < M) {
                     __half* dst = y + (size_t)row * N + n0 + c0;
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         if (n0 + c0 + 8 * j < N) {  // N is a multiple of 8
-                            uint32_t w[4];
+                            float v[8];
 #pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const __half2 h = __floats2half2_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
-                                w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                            for (int e = 0; e < 8; e++) v[e] = __uint_as_float(r[8 * j + e]);
+                            if (epi.resid) {
+                                float a[8];
+                                Vec16<__half>::load(epi.resid + (size_t)row * N + n0 + c0 + 8 * j, a);
+#pragma unroll
+                                for (int e = 0; e < 8; e++) v[e] += a[e];
+                                if (epi.bias) {
+                                    Vec16<__half>::load(epi.bias + n0 + c0 + 8 * j, a);
+#pragma unroll
+                                    for (int e = 0; e < 8; e++) v[e] += a[e];
+                                }
                             }
-                            *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            const uint4 packed = Vec16<__half>::pack(v);
+                            *reinterpret_cast<uint4*>(dst + 8 * j) = packed;
+                            if (epi.ss_out) {
+                                Vec16<__half>::unpack(packed, v);  // what the next projection will read
+#pragma unroll
+                                for (int e = 0; e < 8; e++) sq = fmaf(v[e], v[e], sq);
+                            }
                         }
                     }
                 }
             }
+            if (epi.ss_out && row < M) epi.ss_out[(size_t)row * tiles_n + n0 / kOutN] = sq;
             // this thread's reads of the accumulator are over: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(acc_empty0 + 8 * acc);
@@ -255,7 +297,8 @@ int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
 int gemm_f16_skinny(const __half* x, const __half* W, __half* y, int M, int N, int K, int w_layout, cudaStream_t st);
 
 // mode 0: W [K,N]; 1: W [N,K]; 2: W and W2 [K,N], y = silu(x.W) * (x.W2)
-static int gemm_tc_launch(const __half* x, const __half* W, const __half* W2, __half* y, int M, int N, int K, int mode, cudaStream_t st)
+static int gemm_tc_launch(const __half* x, const __half* W, const __half* W2, __half* y, int M, int N, int K, int mode, cudaStream_t st,
+                          const TcEpilogue& epi = TcEpilogue{})
 {
     ONELLM_REQUIRE(K % 8 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED, "gemm: M > 64 needs K %% 8 == 0 and N %% 8 == 0 (K=%d N=%d)",
                    K, N);
@@ -279,11 +322,11 @@ static int gemm_tc_launch(const __half* x, const __half* W, const __half* W2, __
     ONELLM_REQUIRE(tiles <= 0x7fffffffL, ONELLM_ERR_UNSUPPORTED, "gemm: too many tiles");
     const dim3 grid((unsigned)std::min<long>(tiles, num_sms()));  // persistent: one block per SM (shared memory allows no more)
     if (mode == 0)
-        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<0>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K));
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<0>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K, epi));
     else if (mode == 1)
-        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<1>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K));
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<1>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K, epi));
     else
-        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<2>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K));
+        ONELLM_CUDA(launch_pdl(gemm_tc_kernel<2>, grid, dim3(kTcThreads), kTcSmemBytes, st, map_a, map_b, map_b2, y, M, N, K, epi));
     return ONELLM_OK;
 }
 
@@ -296,6 +339,22 @@ int gemm_f16_large(const __half* x, const __half* W, __half* y, int M, int N, in
 int gemm_swiglu_f16_large(const __half* x, const __half* Wg, const __half* Wu, __half* out, int M, int I, int K, cudaStream_t st)
 {
     return gemm_tc_launch(x, Wg, Wu, out, M, I, K, 2, st);
+}
+
+// Column tiles of a projection with N outputs (two weights: gate and up share a tile): the second extent of the
+// [M, parts] array of partial row sums that onellm_gemm_rows writes.
+int gemm_rows_parts(int N, bool dual)
+{
+    const int out_n = dual ? kTcBN / 2 : kTcBN;
+    return (N + out_n - 1) / out_n;
+}
+
+// The large-M form of the norm-free projections (see TcEpilogue).
+int gemm_rows_f16(const __half* x, const __half* W, const __half* W2, __half* y, int M, int N, int K, const float* row_ss, int ss_parts,
+                  float eps, const __half* resid, const __half* bias, float* ss_out, cudaStream_t st)
+{
+    const TcEpilogue epi = {row_ss, ss_parts, eps, resid, resid ? bias : nullptr, ss_out};
+    return gemm_tc_launch(x, W, W2, y, M, N, K, W2 ? 2 : 0, st, epi);
 }
 
 int attn_tc_timeout_flag();  // context_attn_tc.cu

@@ -199,6 +199,7 @@ struct Llama {
     char* pf_buf = nullptr;
     size_t pf_tokens = 0;
     bool prefill_by_decode = false;  // true: run the context phase one position at a time (reference path for tests)
+    bool prefill_norm_kernels = false;  // true: keep the norm kernels in the context phase on one GPU too (comparison)
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -498,13 +499,15 @@ static int prefill_context(Llama& m, int B, const int* lens)
     cudaStream_t st = m.stream;
     void* sp = (void*)st;
     // scratch layout for T tokens
-    const size_t per_tok = ((size_t)2 * h + m.qkv_cols + (size_t)m.Hl * D + (size_t)m.Il) * sizeof(__half);
+    const int ss_parts = onellm_gemm_rows_parts(h, 0);  // partial row sums written by the projections that end in the stream
+    const size_t per_tok = ((size_t)2 * h + m.qkv_cols + (size_t)m.Hl * D + (size_t)m.Il) * sizeof(__half) +
+                           ((size_t)2 * ss_parts + 1) * sizeof(float);
     if (T > m.pf_tokens) {
         ONELLM_CUDA(cudaStreamSynchronize(st));
         if (m.pf_buf) cudaFree(m.pf_buf);
         m.pf_buf = nullptr;
         m.pf_tokens = 0;
-        const cudaError_t e = cudaMalloc(&m.pf_buf, T * per_tok + 6 * 256 + (size_t)(2 * c.max_batch + 2) * sizeof(int));
+        const cudaError_t e = cudaMalloc(&m.pf_buf, T * per_tok + 10 * 256 + (size_t)(2 * c.max_batch + 2) * sizeof(int));
         ONELLM_REQUIRE(e == cudaSuccess, ONELLM_ERR_CUDA, "llama_prefill: cannot allocate context scratch for %zu tokens: %s", T,
                        cudaGetErrorString(e));
         m.pf_tokens = T;
@@ -515,6 +518,9 @@ static int prefill_context(Llama& m, int B, const int* lens)
     __half* qkv = cv.take<__half>(T * m.qkv_cols);
     __half* attn = cv.take<__half>(T * (size_t)m.Hl * D);
     __half* act = cv.take<__half>(T * (size_t)m.Il);
+    float* ss0 = cv.take<float>(T);
+    float* ss_a = cv.take<float>(T * ss_parts);
+    float* ss_b = cv.take<float>(T * ss_parts);
     int* d_cu = cv.take<int>(c.max_batch + 1);
     int* d_hist = cv.take<int>(c.max_batch);
     std::vector<int> cu(B + 1, 0), hist(B), off(B);
@@ -532,11 +538,38 @@ static int prefill_context(Llama& m, int B, const int* lens)
     ONELLM_CUDA(cudaStreamSynchronize(st));  // cu / hist / off live on this stack frame
 
     const long launches_before = launches_noted();
+    const long cs_b = (long)m.Hkvl * c.max_seq_len * D, cs_h = (long)c.max_seq_len * D, cs_s = D;
+    const float scale = 1.0f / sqrtf((float)D);
+    const bool norm_free = c.tp_size == 1 && !m.prefill_norm_kernels;
+    if (norm_free) {
+        // One GPU: no norm kernels, as in the decode step.  The residual stream lives in `res`; a projection behind a
+        // norm reads it raw and scales its rows by rsqrt(mean(x^2) + eps) on the way out (the gammas are inside the
+        // weights), o_proj and down_proj add their result to the stream in their epilogue and leave, per column tile,
+        // the sum of squares of what they stored: the row statistics of the next projection.
+        RC(embedding_launch(ONELLM_F16, m.d_prompt, res, nullptr, m.tok_emb, (int)T, h, c.vocab_size, m.d_bad_id, false, st));
+        RC(onellm_row_sumsq(ONELLM_F16, res, (int)T, h, ss0, sp));
+        for (int l = 0; l < c.num_layers; l++) {
+            const LayerW& L = m.layers[l];
+            __half* kc = m.k_cache + (size_t)l * m.cache_layer_elems;
+            __half* vc = m.v_cache + (size_t)l * m.cache_layer_elems;
+            RC(onellm_gemm_rows(ONELLM_F16, res, L.w_qkv, nullptr, qkv, (int)T, m.qkv_cols, h, l == 0 ? ss0 : ss_a, l == 0 ? 1 : ss_parts,
+                                c.rms_eps, nullptr, nullptr, nullptr, sp));
+            RC(onellm_qkv_bias_rope_kvcache(ONELLM_F16, qkv, L.b_qkv, d_cu, d_hist, kc, vc, cs_b, cs_h, cs_s, (int)T, B, m.Hl, m.Hkvl,
+                                            D, c.rot_dim, c.rope_base, c.max_seq_len, m.d_bad_id + 1, sp));
+            RC(onellm_context_attn(ONELLM_F16, qkv, m.qkv_cols, kc, vc, cs_b, cs_h, cs_s, d_cu, d_hist, B, P, m.Hl, m.Hkvl, D, scale,
+                                   attn, sp));
+            RC(onellm_gemm_rows(ONELLM_F16, attn, L.wo, nullptr, res, (int)T, h, m.Hl * D, nullptr, 0, c.rms_eps, res, L.b_o, ss_b, sp));
+            RC(onellm_gemm_rows(ONELLM_F16, res, L.w1, L.w3, act, (int)T, m.Il, h, ss_b, ss_parts, c.rms_eps, nullptr, nullptr, nullptr, sp));
+            RC(onellm_gemm_rows(ONELLM_F16, act, L.w2, nullptr, res, (int)T, h, m.Il, nullptr, 0, c.rms_eps, res, nullptr, ss_a, sp));
+        }
+        // last position of every sequence: the final norm (not folded), LM head, top-K, sampling
+        note_launch();
+        gather_last_rows_kernel<<<B, 256, 0, st>>>(res, d_cu, m.y, h);
+        RC(onellm_rmsnorm(ONELLM_F16, m.y, m.out_norm, c.rms_eps, B, h, sp));
+    } else {
     // d_prompt holds the new tokens packed in sequence order
     RC(embedding_launch(ONELLM_F16, m.d_prompt, y, res, m.tok_emb, (int)T, h, c.vocab_size, m.d_bad_id, false, st));
     RC(onellm_rmsnorm(ONELLM_F16, y, m.layers[0].attn_norm, c.rms_eps, (int)T, h, sp));
-    const long cs_b = (long)m.Hkvl * c.max_seq_len * D, cs_h = (long)c.max_seq_len * D, cs_s = D;
-    const float scale = 1.0f / sqrtf((float)D);
     for (int l = 0; l < c.num_layers; l++) {
         const LayerW& L = m.layers[l];
         __half* kc = m.k_cache + (size_t)l * m.cache_layer_elems;
@@ -559,6 +592,7 @@ static int prefill_context(Llama& m, int B, const int* lens)
     // position-by-position path does)
     note_launch();
     gather_last_rows_kernel<<<B, 256, 0, st>>>(y, d_cu, m.y, h);
+    }
     RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, m.head_layout, sp));
     RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
     RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
@@ -707,7 +741,8 @@ extern "C" int onellm_llama_set_prefill_by_decode(onellm_llama* h, int enabled)
 {
     Llama* m = reinterpret_cast<Llama*>(h);
     ONELLM_REQUIRE(m, ONELLM_ERR_ARG, "llama_set_prefill_by_decode: null handle");
-    m->prefill_by_decode = enabled != 0;
+    m->prefill_by_decode = enabled == 1;
+    m->prefill_norm_kernels = enabled == 2;
     return ONELLM_OK;
 }
 

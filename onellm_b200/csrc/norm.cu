@@ -137,6 +137,39 @@ static int check_norm_args(const char* who, int dtype, const void* x, const void
 
 using namespace onellm;
 
+namespace onellm {
+// out[row] = sum of squares of the fp16 row: the row statistics the norm-free context-phase projections take as an
+// input (one warp per row)
+__global__ void __launch_bounds__(256) row_sumsq_kernel(const __half* __restrict__ x, float* __restrict__ out, int rows, int cols)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const __half* xr = x + (size_t)row * cols;
+    float s = 0.f;
+    for (int i = lane; i < cols / 8; i += 32) {
+        float v[8];
+        Vec16<__half>::load(xr + (size_t)i * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; e++) s = fmaf(v[e], v[e], s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) out[row] = s;
+}
+}  // namespace onellm
+
+extern "C" int onellm_row_sumsq(int dtype, const void* x, int rows, int cols, float* out, void* stream)
+{
+    ONELLM_REQUIRE(x && out, ONELLM_ERR_ARG, "row_sumsq: null pointer");
+    ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "row_sumsq: only F16 is implemented");
+    ONELLM_REQUIRE(rows >= 0 && cols > 0 && cols % 8 == 0 && aligned16(x), ONELLM_ERR_ARG, "row_sumsq: rows of whole 16-byte vectors");
+    if (rows == 0) return ONELLM_OK;
+    ONELLM_CUDA(launch_pdl(onellm::row_sumsq_kernel, dim3((rows + 7) / 8), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                           (const __half*)x, out, rows, cols));
+    return ONELLM_OK;
+}
+
 extern "C" int onellm_rmsnorm(int dtype, void* x, const void* gamma, float eps, int num_tokens, int hidden,
                               void* stream)
 {

@@ -292,6 +292,31 @@ extern "C" int onellm_gemm_fused(int dtype, const void* x, const void* W, const 
     return ONELLM_OK;
 }
 
+namespace onellm {
+int gemm_rows_parts(int N, bool dual);  // gemm_tc.cu
+int gemm_rows_f16(const __half* x, const __half* W, const __half* W2, __half* y, int M, int N, int K, const float* row_ss, int ss_parts,
+                  float eps, const __half* resid, const __half* bias, float* ss_out, cudaStream_t st);
+}  // namespace onellm
+
+extern "C" int onellm_gemm_rows_parts(int N, int dual) { return N > 0 ? onellm::gemm_rows_parts(N, dual != 0) : 0; }
+
+extern "C" int onellm_gemm_rows(int dtype, const void* x, const void* W, const void* Wu, void* y, int M, int N, int K, const float* row_ss,
+                                int ss_parts, float rms_eps, const void* resid, const void* bias, float* row_ss_out, void* stream)
+{
+    ONELLM_REQUIRE(x && W && y, ONELLM_ERR_ARG, "gemm_rows: null pointer");
+    ONELLM_REQUIRE(dtype == ONELLM_F16, ONELLM_ERR_UNSUPPORTED, "gemm_rows: only F16 is implemented");
+    ONELLM_REQUIRE(M >= 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0, ONELLM_ERR_UNSUPPORTED, "gemm_rows: need K %% 8 == 0 and N %% 8 == 0");
+    ONELLM_REQUIRE(!row_ss || ss_parts >= 1, ONELLM_ERR_ARG, "gemm_rows: row_ss needs its number of partial sums per row");
+    ONELLM_REQUIRE(resid || !bias, ONELLM_ERR_ARG, "gemm_rows: bias is added with the residual; pass resid too");
+    ONELLM_REQUIRE(!(Wu && (resid || row_ss_out)), ONELLM_ERR_UNSUPPORTED, "gemm_rows: the gate/up form takes neither resid nor row_ss_out");
+    ONELLM_REQUIRE(aligned16(x) && aligned16(W) && aligned16(y) && (!Wu || aligned16(Wu)) && (!resid || aligned16(resid)) &&
+                       (!bias || aligned16(bias)) && x != y,
+                   ONELLM_ERR_ARG, "gemm_rows: pointers must be 16-byte aligned and y must not alias x");
+    if (M == 0) return ONELLM_OK;
+    return onellm::gemm_rows_f16((const __half*)x, (const __half*)W, (const __half*)Wu, (__half*)y, M, N, K, row_ss, ss_parts, rms_eps,
+                                 (const __half*)resid, (const __half*)bias, row_ss_out, reinterpret_cast<cudaStream_t>(stream));
+}
+
 extern "C" int onellm_gemm_swiglu(int dtype, const void* x, const void* Wg, const void* Wu, void* out, int M,
                                   int I, int K, void* stream)
 {

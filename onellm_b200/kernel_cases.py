@@ -18,8 +18,8 @@ Context-phase cases (reported in TFLOP/s, except prefill_rope):
     prefill_qkv, prefill_o, prefill_gate, prefill_down, prefill_lm     projections on --batch x --ctx token rows
     prefill_attn                   causal attention of --batch sequences x --ctx tokens
     prefill_rope                   bias + RoPE + KV-cache write (GB/s)
-    prefill_layer                  one whole decoder layer on --batch x --ctx tokens: QKV projection, RoPE + cache write,
-                                   attention, o_proj, add-residual RMSNorm, gate/up + SwiGLU, down, add-residual RMSNorm
+    prefill_layer                  one whole decoder layer on --batch x --ctx tokens as the model runs it: QKV projection (RMS scale
+                                   in its epilogue), RoPE + cache write, attention, o_proj (+ residual), gate/up + SwiGLU, down (+ residual)
 
 Every case holds a few hundred MB on the device (more than the 126 MB L2, far less than a model) and runs on
 rotating buffers.  `--tp T` uses the per-rank shapes of T-way tensor parallelism; `--graph` times the launches as
@@ -231,22 +231,25 @@ def make_case(name, torch, model="7b", batch=8, ctx=2040, tp=1, plain=False) -> 
         kc, vc = torch.zeros(B, H, S, D, **half), torch.zeros(B, H, S, D, **half)
         flag = torch.zeros(1, device="cuda", dtype=torch.int32)
 
+        n_parts = ob.gemm_rows_parts(HID)
+        ss_a = torch.ones(T, n_parts, device="cuda", dtype=torch.float32)
+        ss_b = torch.ones(T, n_parts, device="cuda", dtype=torch.float32)
+
         def fn(i):
-            # the sequence LlamaContextDecoder::forward runs for one layer (src/layers/decoder/context_decoder.cpp:95-131),
-            # from the normalised input to the add-residual RMSNorm in front of the next layer
-            ob.gemm(F16, x0, w_qkv[i], qkv, T, 3 * H * D, HID, ob.W_KN)
+            # one layer of the context phase as the model runs it on one GPU: what LlamaContextDecoder::forward does per layer
+            # (src/layers/decoder/context_decoder.cpp:95-131) without norm kernels -- the projections behind a norm scale their
+            # rows from the statistics the projection before them left, o_proj and down_proj add into the residual stream
+            ob.gemm_rows(F16, res, w_qkv[i], None, qkv, T, 3 * H * D, HID, row_ss=ss_a, ss_parts=n_parts)
             ob.qkv_bias_rope_kvcache(F16, qkv, None, cu, hl, kc, vc, H * S * D, S * D, D, T, B, H, H, D, D, 10000.0, S, flag)
             ob.context_attn(F16, qkv, 3 * H * D, kc, vc, H * S * D, S * D, D, cu, hl, B, P, H, H, D, D ** -0.5, attn)
-            ob.gemm(F16, attn, w_o[i], y, T, HID, H * D, ob.W_KN)
-            ob.add_residual_rmsnorm(F16, res, y, None, g, 1e-5, T, HID)
-            ob.gemm_swiglu(F16, y, w_g[i], w_u[i], a, T, INTER, HID)
-            ob.gemm(F16, a, w_d[i], y, T, HID, INTER, ob.W_KN)
-            ob.add_residual_rmsnorm(F16, res, y, None, g, 1e-5, T, HID)
+            ob.gemm_rows(F16, attn, w_o[i], None, res, T, HID, H * D, resid=res, row_ss_out=ss_b)
+            ob.gemm_rows(F16, res, w_g[i], w_u[i], a, T, INTER, HID, row_ss=ss_b, ss_parts=n_parts)
+            ob.gemm_rows(F16, a, w_d[i], None, res, T, HID, INTER, resid=res, row_ss_out=ss_a)
 
         # dense flops: projections + both attention products over the full square (the causal half is skipped)
         flops = 2.0 * T * HID * (3 * H * D + H * D) + 6.0 * T * HID * INTER + 4.0 * B * H * D * P * P
-        return Case(fn, rot, flops, "flop", "gemm_tc_kernel", launches=8,
-                    keep=(w_qkv, w_o, w_g, w_u, w_d, g, x0, y, res, qkv, attn, a, kc, vc, flag, cu, hl))
+        return Case(fn, rot, flops, "flop", "gemm_tc_kernel", launches=6,
+                    keep=(w_qkv, w_o, w_g, w_u, w_d, g, x0, y, res, qkv, attn, a, kc, vc, flag, cu, hl, ss_a, ss_b))
     raise ValueError(f"unknown case {name}")
 
 

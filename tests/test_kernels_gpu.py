@@ -525,3 +525,40 @@ def test_gemm_tensor_core_weight_streaming_kernel(ob, cuda, orc, M, N, K, dual, 
         assert torch.equal(outs[0], outs[1])
     finally:
         ob.gemm_tc_min_tokens(before)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 512, 256), (1024, 4096, 4096), (130, 1000, 528)])
+def test_gemm_rows_norm_free_context_projections(ob, cuda, orc, M, N, K):
+    """onellm_gemm_rows: row scale from partial sums of squares, residual + bias in the epilogue, and the partial sums of
+    squares of what was stored (the next projection's input statistics); onellm_row_sumsq."""
+    torch = cuda
+    rng = np.random.default_rng(M + N)
+    x = _round(3.0 * rng.standard_normal((M, K)), "f16")
+    W = _round(0.02 * rng.standard_normal((K, N)), "f16")
+    Wu = _round(0.02 * rng.standard_normal((K, N)), "f16")
+    r = _round(rng.standard_normal((M, N)), "f16")
+    b = _round(0.1 * rng.standard_normal(N), "f16")
+    d_x, d_W, d_Wu = _dev(torch, x, "f16"), _dev(torch, W, "f16"), _dev(torch, Wu, "f16")
+    ss = torch.zeros(M, device="cuda", dtype=torch.float32)
+    ob.row_sumsq(ob.F16, d_x, M, K, ss)
+    want_ss = (x.astype(np.float64) ** 2).sum(axis=1)
+    assert rel_err(ss.cpu().numpy(), want_ss) < 1e-5
+    inv = 1.0 / np.sqrt(want_ss[:, None] / K + 1e-5)
+    # (1) RMS scale; the row sums handed over as three partial sums per row
+    parts = torch.stack([0.5 * ss, 0.25 * ss, 0.25 * ss], dim=1).contiguous()
+    y = torch.zeros(M, N, device="cuda", dtype=torch.float16)
+    ob.gemm_rows(ob.F16, d_x, d_W, None, y, M, N, K, row_ss=parts, ss_parts=3, rms_eps=1e-5)
+    assert rel_err(y.float().cpu().numpy(), orc.gemm(x, W) * inv) < TOL["f16"]
+    # (2) gate/up + SwiGLU behind the same scale
+    ob.gemm_rows(ob.F16, d_x, d_W, d_Wu, y, M, N, K, row_ss=ss, ss_parts=1, rms_eps=1e-5)
+    ref = orc.swiglu2((orc.gemm(x, W) * inv).astype(np.float32), (orc.gemm(x, Wu) * inv).astype(np.float32))
+    assert rel_err(y.float().cpu().numpy(), ref) < TOL["f16"]
+    # (3) residual + bias added in place, and the statistics of the stored rows
+    n_parts = ob.gemm_rows_parts(N)
+    y = _dev(torch, r, "f16")
+    ss_out = torch.full((M, n_parts), -1.0, device="cuda", dtype=torch.float32)
+    ob.gemm_rows(ob.F16, d_x, d_W, None, y, M, N, K, resid=y, bias=_dev(torch, b, "f16"), row_ss_out=ss_out)
+    got = y.float().cpu().numpy()
+    assert rel_err(got, orc.gemm(x, W) + r + b) < TOL["f16"]
+    assert rel_err(ss_out.sum(dim=1).cpu().numpy(), (got.astype(np.float64) ** 2).sum(axis=1)) < 1e-5   # of the ROUNDED values
+    assert ob.lib().onellm_gemm_timeout_flag() == 0

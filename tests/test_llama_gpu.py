@@ -127,6 +127,24 @@ def test_second_turn_with_history_matches_one_long_prompt(ob, cuda, orc, tmp_pat
     m.close()
 
 
+def test_norm_free_context_phase_matches_the_one_with_norm_kernels(ob, cuda, tmp_path):
+    """One GPU runs the context phase without norm kernels (row statistics handed from projection to projection);
+    mode 2 keeps the norm kernels, as tensor-parallel runs do.  Same model, same prompt."""
+    cfg = dict(CFG, max_seq_len=160)
+    m, w = _make(ob, tmp_path, cfg, seed=13, attn_bias=True)
+    prompt = np.random.default_rng(4).integers(0, cfg["vocab_size"], (3, 140)).astype(np.int32)
+    m.set_prefill_by_decode(2)
+    m.prefill(prompt)
+    la = m.logits(3)
+    m.set_prefill_by_decode(0)
+    m.prefill(prompt)
+    lb = m.logits(3)
+    m.prefill(prompt)
+    assert np.array_equal(m.logits(3), lb)      # no atomics: the same bits every time
+    assert rel_err(lb, la) < 3e-3
+    m.close()
+
+
 def test_context_phase_matches_position_by_position(ob, cuda, tmp_path):
     """A 100-token prompt (tensor-core GEMMs, M = 300) against the same prompt fed one position at a time."""
     cfg = dict(CFG, max_seq_len=128)
