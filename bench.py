@@ -54,9 +54,14 @@ METRIC = "decode tokens/s (Llama-7B shape, 1/2/4/8 B200); attn HBM GB/s vs peak"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures of single kernels, keyed by
 # (model, batch, tensor-parallel degree, kernel case); each entry names the summary under profiles/ it comes from
 NCU_TRAFFIC = {
-    ("7b", 8, 1, "gate_up"): (184_805_632, "profiles/skinny_kn_staged_gate_up_m8_4096x11008.md (180.45 MB read + 4.36 MB written; "
-                                           "plain variant of the kernel, same weight stream)"),
-    ("7b", 8, 1, "down"): (93_978_112, "profiles/skinny_kn_staged_down_m8_11008x4096.md"),
+    ("7b", 8, 1, "gate_up"): (184_644_078, "profiles/skinny_kn_staged_decode_projections_7b_m8.md"),
+    ("7b", 8, 1, "qkv"): (104_611_591, "profiles/skinny_kn_staged_decode_projections_7b_m8.md"),
+    ("7b", 8, 1, "o_proj"): (33_713_661, "profiles/skinny_kn_staged_decode_projections_7b_m8.md"),
+    ("7b", 8, 1, "down"): (94_489_093, "profiles/skinny_kn_staged_decode_projections_7b_m8.md"),
+    ("7b", 8, 1, "decode_attn_ctx2040"): (272_267_275, "profiles/decode_attn_mma_f16_b8_h32_ctx2040.md"),
+    ("7b", 8, 1, "decode_attn_ctx520"): (68_822_524, "profiles/decode_attn_mma_f16_b8_h32_ctx2040.md"),
+    ("13b", 64, 1, "qkv"): (161_732_628, "profiles/skinny_tc_kernel_13b_m64.md"),
+    ("13b", 64, 1, "gate_up"): (287_671_566, "profiles/skinny_tc_kernel_13b_m64.md"),
 }
 
 

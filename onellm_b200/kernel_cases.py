@@ -55,6 +55,14 @@ class Case:
     keep: tuple = ()            # buffers kept alive
 
 
+def _projection_kernel(tokens, dual):
+    """Name of the kernel a [K, N] projection of `tokens` rows runs on."""
+    if tokens >= ob.gemm_tc_min_tokens() and tokens <= 64:
+        return f"skinny_tc_kernel<{'true' if dual else 'false'}>"
+    mb = 1 if tokens <= 8 else 2 if tokens <= 16 else 4 if tokens <= 32 else 8
+    return f"skinny_kn_staged_kernel<{mb},{'true' if dual else 'false'},false>"
+
+
 def make_case(name, torch, model="7b", batch=8, ctx=2040, tp=1, plain=False) -> Case:
     m = MODELS[model] if isinstance(model, str) else model
     HID, D, V = m["hidden"], m["head_size"], m["vocab_size"]
@@ -80,7 +88,7 @@ def make_case(name, torch, model="7b", batch=8, ctx=2040, tp=1, plain=False) -> 
         else:  # as in the decode step: raw residual stream in, scaled by rsqrt(mean(x^2) + eps) on the way out
             fn = lambda i: ob.gemm_fused(F16, x, w[i], wu[i], out, B, N, HID, 1e-5, None, None)
         nbytes = (2 if dual else 1) * HID * N * 2 + B * HID * 2 + B * N * 2
-        kern = f"skinny_kn_staged_kernel<{(B + 7) // 8},{'true' if dual else 'false'},{'false' if plain else 'true'}>"
+        kern = _projection_kernel(B, dual)
         return Case(fn, rot, nbytes, "B", kern, keep=(x, w, wu, out))
     if name in ("o_proj", "down"):
         K = H * D if name == "o_proj" else INTER
@@ -93,7 +101,7 @@ def make_case(name, torch, model="7b", batch=8, ctx=2040, tp=1, plain=False) -> 
         else:  # as in the decode step: the result is added to the residual stream in the epilogue
             fn = lambda i: ob.gemm_fused(F16, x, w[i], None, res, B, HID, K, -1.0, res, None)
         nbytes = K * HID * 2 + B * K * 2 + (1 if plain else 2) * B * HID * 2
-        return Case(fn, rot, nbytes, "B", f"skinny_kn_staged_kernel<{(B + 7) // 8},false,false>", keep=(x, w, res, out))
+        return Case(fn, rot, nbytes, "B", _projection_kernel(B, False), keep=(x, w, res, out))
     if name in ("lm_head", "lm_head_kn"):
         lay = ob.W_NK if name == "lm_head" else ob.W_KN
         rot = 2
@@ -101,7 +109,7 @@ def make_case(name, torch, model="7b", batch=8, ctx=2040, tp=1, plain=False) -> 
         w = [rnd(V, HID) if lay == ob.W_NK else rnd(HID, V) for _ in range(rot)]
         out = torch.empty(B, V, **half)
         fn = lambda i: ob.gemm(F16, x, w[i], out, B, V, HID, lay)
-        kern = "skinny_nk_kernel" if lay == ob.W_NK else f"skinny_kn_staged_kernel<{(B + 7) // 8},false,false>"
+        kern = "skinny_nk_kernel" if lay == ob.W_NK else _projection_kernel(B, False)
         return Case(fn, rot, V * HID * 2 + B * HID * 2 + B * V * 2, "B", kern, keep=(x, w, out))
     if name == "attn":
         S = ctx + 8
