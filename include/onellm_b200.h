@@ -484,6 +484,12 @@ ONELLM_API int onellm_llama_p2p_error(onellm_llama* m);
  * run of src/layers/decoder/self_decoder.cpp:47-73 needs behind o_proj and down_proj; the switch lets a caller
  * (the benchmark's result check) run the same steps both ways.  Every rank must choose the same. */
 ONELLM_API int onellm_llama_set_tp_exchange(onellm_llama* m, int peer_memory);
+/* The uniform draws of the last sampling launch (host_u: max_batch floats) and the step counter they were
+ * seeded with: row b drew curand_uniform of curand_init(step, b, 0), the generator of src/kernels/topK_sampling.cu:29-30.
+ * The engine takes the skip-ahead to sub-sequence b from a table built (and checked against curand_init) when the
+ * model was created; *table_in_use (may be NULL) says whether that table passed its check.  host_step may be
+ * NULL.  Waits for the model's stream. */
+ONELLM_API int onellm_llama_last_draws(onellm_llama* m, float* host_u, int* host_step, int* table_in_use);
 /* 1: run the context phase one position at a time through the decode kernels (cross-check path);
  * 0 (default): all prompt tokens at once through the context-phase kernels; 2: the same with the norm kernels
  * kept between the projections on one GPU too (what tensor-parallel runs always do; comparison). */

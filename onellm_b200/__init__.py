@@ -381,6 +381,15 @@ class Llama:
     def p2p_error(self) -> int:
         return int(lib().onellm_llama_p2p_error(self._h))
 
+    def last_draws(self):
+        """(u, step, table_in_use): the uniform draws of the last sampling launch (numpy float32 [max_batch]), the step
+        counter that seeded them and whether the engine's skip-ahead table is in use."""
+        import numpy as np
+        u = np.zeros(self.cfg.max_batch, np.float32)
+        step, used = C.c_int(0), C.c_int(0)
+        _check(lib().onellm_llama_last_draws(self._h, u.ctypes.data_as(C.c_void_p), C.byref(step), C.byref(used)))
+        return u, step.value, bool(used.value)
+
     def set_sampling(self, top_k=1, temperature=1.0, literal_walk=False):
         _check(lib().onellm_llama_set_sampling(self._h, C.c_int(top_k), C.c_float(temperature),
                                                C.c_int(1 if literal_walk else 0)))

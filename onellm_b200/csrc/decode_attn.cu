@@ -731,7 +731,7 @@ static AttnPlan plan_attention_mma(int B, int n_head_blocks, int step, int D, in
     AttnPlan best = {1, rows_all, 2, 2 * kMmaWarps * tile};
     double best_t = 1.0e300;
     const double bytes = 2.0 * (double)n_cached * (double)base * D * 2.0;
-    constexpr double kPeak = 6.5e12, kLatency = 2.3e-6, kWaveCost = 1.0e-6, kMergeCost = 3.0e-6;
+    constexpr double kPeak = 6.5e12, kLatency = 2.3e-6, kWaveCost = 1.0e-6, kMergeCost = 6.0e-6;  // the merge kernel costs a launch boundary in a step, not only its run time
     const double t_tile = 0.9e-6 * (double)D / 128.0;
     // Two blocks per SM (three stages per warp at D = 128) won or tied every sweep over (blocks per SM, splits) on B200,
     // from 32 to 2560 (sequence, head) pairs and 520 to 2040 rows: three blocks leave one tile in flight per warp, one

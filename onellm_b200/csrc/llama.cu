@@ -175,6 +175,8 @@ struct Llama {
     std::vector<int> seq_off;  // host copy
     unsigned char* d_finished = nullptr;
     float *d_topk_val = nullptr, *d_u = nullptr;
+    uint32_t* d_skip = nullptr;  // the sampler's per-row skip-ahead table (sampling.cu)
+    int skip_ok = 0;             // 1 once the table is built and has matched the direct draws
     __half *res = nullptr, *y = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr,
            *logits = nullptr;
     void* attn_ws = nullptr;
@@ -203,6 +205,10 @@ struct Llama {
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// sampling.cu: the sampler's per-row skip-ahead table
+size_t skip_table_words(int rows);
+int build_skip_table(uint32_t* table, int rows, int* usable, cudaStream_t st);
 
 struct Carver {
     char* base;
@@ -252,6 +258,7 @@ static void carve(Llama& m, Carver& cv)
     m.d_finished = cv.take<unsigned char>(B);
     m.d_topk_val = cv.take<float>(B * 64);
     m.d_u = cv.take<float>(B);
+    m.d_skip = cv.take<uint32_t>(skip_table_words((int)B));
     m.res = cv.take<__half>(B * h);
     m.y = cv.take<__half>(B * h);
     m.qkv = cv.take<__half>(B * m.qkv_cols);
@@ -271,7 +278,7 @@ int embedding_launch(int dtype, const int* ids, void* out, void* out2, const voi
 int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, float temperature, int rng_step,
                        const int* rng_step_dev, int vocab_size, int end_id, int literal_walk, int* output_id,
                        int* seqlen, unsigned char* finished, float* u_out, int* output_id2, bool early_seed,
-                       cudaStream_t st);
+                       const uint32_t* skip_table, cudaStream_t st);
 
 #define RC(call)              \
     do {                      \
@@ -405,7 +412,8 @@ static int enqueue_step(Llama& m, int mode, int step_bound, int prompt_len)
         RC(onellm_gemm(ONELLM_F16, head_in, m.out_w, m.logits, B, c.vocab_size, h, m.head_layout, sp));
         RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
         RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size,
-                              c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
+                              c.eos_id, m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true,
+                              m.skip_ok ? m.d_skip : nullptr, st));
     }
     ONELLM_CHECK_LAUNCH();
     return ONELLM_OK;
@@ -596,7 +604,8 @@ static int prefill_context(Llama& m, int B, const int* lens)
     RC(onellm_gemm(ONELLM_F16, m.y, m.out_w, m.logits, B, c.vocab_size, h, m.head_layout, sp));
     RC(onellm_topk(ONELLM_F16, m.logits, B, c.vocab_size, m.top_k, m.d_topk_val, m.d_topk_id, 0, sp));
     RC(topk_sample_launch(m.d_topk_id, m.d_topk_val, B, m.top_k, m.temperature, 0, m.d_step, c.vocab_size, c.eos_id,
-                          m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true, st));
+                          m.literal_walk, m.d_out_ids, m.d_seqlen, m.d_finished, m.d_u, m.d_ids, /*early_seed=*/true,
+                          m.skip_ok ? m.d_skip : nullptr, st));
     m.launches += launches_noted() - launches_before;
     for (int b = 0; b < B; b++) m.seq_off[b] = off[b];
     m.cur_len = new_max;
@@ -712,13 +721,30 @@ extern "C" int onellm_llama_create(const onellm_llama_config* cfg, onellm_llama*
     if (e == cudaSuccess) e = cudaMemsetAsync(m->d_step, 0, 4 * sizeof(int), m->stream);
     if (e == cudaSuccess) e = cudaMemsetAsync(m->d_bad_id, 0, 4 * sizeof(int), m->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    if (e == cudaSuccess && build_skip_table(m->d_skip, m->c.max_batch, &m->skip_ok, m->stream) != ONELLM_OK)
+        e = cudaErrorUnknown;  // the text is already in the error slot
     if (e != cudaSuccess) {
-        set_error("llama_create: %s", cudaGetErrorString(e));
+        if (e != cudaErrorUnknown) set_error("llama_create: %s", cudaGetErrorString(e));
+        if (m->stream) cudaStreamDestroy(m->stream);
         cudaFree(m->arena);
         delete m;
         return ONELLM_ERR_CUDA;
     }
     *out = reinterpret_cast<onellm_llama*>(m);
+    return ONELLM_OK;
+}
+
+extern "C" int onellm_llama_last_draws(onellm_llama* h, float* host_u, int* host_step, int* table_in_use)
+{
+    Llama* m = reinterpret_cast<Llama*>(h);
+    ONELLM_REQUIRE(m && host_u, ONELLM_ERR_ARG, "llama_last_draws: null pointer");
+    ONELLM_CUDA(cudaMemcpyAsync(host_u, m->d_u, (size_t)m->c.max_batch * sizeof(float), cudaMemcpyDeviceToHost,
+                                m->stream));
+    int step = 0;
+    ONELLM_CUDA(cudaMemcpyAsync(&step, m->d_step, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    ONELLM_CUDA(cudaStreamSynchronize(m->stream));
+    if (host_step) *host_step = step;
+    if (table_in_use) *table_in_use = m->skip_ok;
     return ONELLM_OK;
 }
 

@@ -178,6 +178,7 @@ __device__ __forceinline__ float key_value<__half>(uint32_t k)
 }
 
 constexpr int kTopkPer = 32;  // keys per thread held in registers
+constexpr int kTopkCand = 512;  // gathered keys the short way ranks; >= kMaxK
 
 // warp-aggregated histogram update: lanes with the same digit elect one to add their count
 __device__ __forceinline__ void hist_add(int* hist, bool pred, uint32_t digit)
@@ -198,13 +199,10 @@ topk_reg_kernel(const T* __restrict__ logits, int vocab, int K, float* __restric
     pdl_wait();
     const int row = blockIdx.x;
     const T* x = logits + (size_t)row * vocab;
-    __shared__ int hist[256];
-    __shared__ uint32_t s_prefix;
-    __shared__ int s_need, s_count;
+    __shared__ int s_count;
     __shared__ int warp_tot[kTopkThreads / 32];
-    __shared__ uint32_t cand_key[kMaxK];
-    __shared__ int cand_id[kMaxK];
-    constexpr int kPasses = sizeof(T) == 2 ? 2 : 4;
+    __shared__ uint32_t cand_key[kTopkCand];
+    __shared__ int cand_id[kTopkCand];
 
     // thread t owns columns [t*32, t*32 + 32): a contiguous slice, so ranks inside a tie follow the columns
     const int c0 = threadIdx.x * kTopkPer;
@@ -223,53 +221,86 @@ topk_reg_kernel(const T* __restrict__ logits, int vocab, int K, float* __restric
 #pragma unroll
         for (int j = 0; j < kTopkPer; j++) key[j] = j < n_mine ? logit_key<T>(x[c0 + j]) : 0u;
     }
-    if (threadIdx.x == 0) {
-        s_prefix = 0u;
-        s_need = K;
-        s_count = 0;
-    }
+    if (threadIdx.x == 0) s_count = 0;
     __syncthreads();
 
-    // 1. K-th largest key, 8 bits at a time from the top
+    constexpr int kLowBit = sizeof(T) == 2 ? 16 : 0;  // fp16 keys live in the upper half
+    __shared__ int bit_tot[2][kTopkThreads / 32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int it = 0;
+
+    // 0. The short way, which nearly every row of logits takes.  The K-th largest of the 1024 per-thread maxima is
+    // a lower bound of the K-th largest key (K threads hold a key that large), and for logits hardly more than K
+    // keys reach it.  One bisection over ONE key per thread finds it (a ballot per warp, one block barrier per bit);
+    // the keys that reach it are gathered (a few dozen shared-memory atomics) and ranked against each other, larger
+    // key first, lower column first among equals: rank r < K is output slot r.  Rows with many equal keys, where
+    // the gathered set would be large, take the bisection over all keys below instead.
+    {
+        uint32_t mk = 0u;  // padding and NaN have key 0
+#pragma unroll
+        for (int j = 0; j < kTopkPer; j++) mk = max(mk, key[j]);
+        uint32_t low = 0u;
 #pragma unroll 1
-    for (int pass = 0; pass < kPasses; pass++) {
-        const int shift = 24 - 8 * pass;
-        const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-        for (int i = threadIdx.x; i < 256; i += kTopkThreads) hist[i] = 0;
-        __syncthreads();
-        const uint32_t prefix = s_prefix;
+        for (int bit = 31; bit >= kLowBit; bit--, it++) {
+            const uint32_t t = low | (1u << bit);
+            const int c = __popc(__ballot_sync(0xffffffffu, mk >= t));
+            if (lane == 0) bit_tot[it & 1][wid] = c;
+            __syncthreads();
+            if (__reduce_add_sync(0xffffffffu, bit_tot[it & 1][lane]) >= K) low = t;
+        }
+        if (mk >= low) {
 #pragma unroll
-        for (int j = 0; j < kTopkPer; j++) hist_add(hist, j < n_mine && (key[j] & mask) == prefix, (key[j] >> shift) & 255u);
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            // warp 0 walks the 256 bins from the top: lane l owns bins 255-8l .. 248-8l
-            int mine = 0;
-#pragma unroll
-            for (int q = 0; q < 8; q++) mine += hist[255 - 8 * (int)threadIdx.x - q];
-            int incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(0xffffffffu, incl, o);
-                if ((int)threadIdx.x >= o) incl += v;
-            }
-            const int need = s_need;
-            const int before = incl - mine;  // keys in bins above this lane's
-            // the lane whose bins contain the need-th key; bin 0 takes whatever is left
-            const bool here = before < need && (incl >= need || threadIdx.x == 31);
-            if (here) {
-                int left = need - before, b = 255 - 8 * (int)threadIdx.x;
-                for (int q = 0; q < 8; q++, b--) {
-                    if (hist[b] >= left || b == 0) break;
-                    left -= hist[b];
+            for (int j = 0; j < kTopkPer; j++) {
+                if (j < n_mine && key[j] >= low) {
+                    const int pos = atomicAdd(&s_count, 1);
+                    if (pos < kTopkCand) {
+                        cand_key[pos] = key[j];
+                        cand_id[pos] = c0 + j;
+                    }
                 }
-                s_prefix = prefix | ((uint32_t)b << shift);
-                s_need = left;
             }
         }
         __syncthreads();
+        const int n_c = s_count;  // >= K: K threads hold a real key >= low (or low == 0 and every column counts)
+        if (n_c <= kTopkCand) {
+            if ((int)threadIdx.x < n_c) {
+                const uint32_t k = cand_key[threadIdx.x];
+                const int id = cand_id[threadIdx.x];
+                int r = 0;
+                for (int j = 0; j < n_c; j++) r += (cand_key[j] > k) || (cand_key[j] == k && cand_id[j] < id);
+                if (r < K) {
+                    out_val[(size_t)row * K + r] = (k == 0u) ? -INFINITY : key_value<T>(k);
+                    out_id[(size_t)row * K + r] = global_ids ? row * vocab + id : id;
+                }
+            }
+            return;
+        }
+        __syncthreads();  // everyone has read s_count
+        if (threadIdx.x == 0) s_count = 0;
+        __syncthreads();
     }
-    const uint32_t kth = s_prefix;
-    const int need_ties = s_need;
+
+    // 1. K-th largest key by bisection on its bits, from the top: the largest t with at least K keys >= t.  Every thread
+    // counts its 32 keys in registers, a warp adds up with one reduction, the 32 warp sums meet in shared memory (two
+    // buffers in turn: one block barrier per bit) and every thread takes the same decision, so nothing is broadcast
+    // and no shared-memory atomic is used (a 256-bin histogram of logits has a handful of hot bins: the radix form
+    // of this step spent most of its 39 us waiting for them).
+    auto block_count = [&](auto pred, int buf) {
+        int c = 0;
+#pragma unroll
+        for (int j = 0; j < kTopkPer; j++) c += (j < n_mine && pred(key[j])) ? 1 : 0;
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (lane == 0) bit_tot[buf][wid] = c;
+        __syncthreads();
+        return __reduce_add_sync(0xffffffffu, bit_tot[buf][lane]);
+    };
+    uint32_t kth = 0u;
+#pragma unroll 1
+    for (int bit = 31; bit >= kLowBit; bit--, it++) {
+        const uint32_t t = kth | (1u << bit);
+        if (block_count([t](uint32_t k) { return k >= t; }, it & 1) >= K) kth = t;
+    }
+    const int need_ties = K - block_count([kth](uint32_t k) { return k > kth; }, it & 1);
 
     // 2. gather: everything above the K-th key (any order), then the lowest-indexed ties
     int ties = 0;
@@ -329,11 +360,89 @@ topk_reg_kernel(const T* __restrict__ logits, int vocab, int K, float* __restric
     }
 }
 
+// The draw of (step, row) is curand_init(step, row, 0) + curand_uniform, as src/kernels/topK_sampling.cu:29-30 of the
+// reference takes it.  For row > 0 nearly all of its time is the skip-ahead to sub-sequence `row`: a linear map
+// (over GF(2)) of the 160 xorshift bits of the XORWOW state, which cuRAND applies bit by bit in one thread, 10-15 us
+// per set bit of the row index.  The map depends on the row only, so a caller that draws for the same rows at
+// every step can have it tabulated once (build_skip_table: the image of each of the 160 unit vectors under
+// skipahead_sequence(row), 3200 bytes per row, and the change of the additive counter `d`); the draw is then
+// curand_init(step, 0, 0), which skips nothing, and an XOR of the columns the state's set bits select, five bits per
+// lane.  The table is checked against the direct form when it is built and not used if a single draw differs.
+constexpr int kSkipBits = 160, kSkipWords = 5;
+constexpr int kSkipRowWords = kSkipBits * kSkipWords + 1;  // a row's columns, then its counter change
+
+__global__ void skip_table_kernel(uint32_t* __restrict__ tab)
+{
+    const int b = blockIdx.x, i = threadIdx.x;  // one row per block, one state bit per thread
+    curandStateXORWOW_t s;
+    s.d = 0u;
+    for (int w = 0; w < kSkipWords; w++) s.v[w] = 0u;
+    s.boxmuller_flag = 0;
+    s.boxmuller_flag_double = 0;
+    s.boxmuller_extra = 0.f;
+    s.boxmuller_extra_double = 0.0;
+    s.v[i >> 5] = 1u << (i & 31);
+    skipahead_sequence((unsigned long long)b, &s);
+    uint32_t* row = tab + (size_t)b * kSkipRowWords;
+    for (int w = 0; w < kSkipWords; w++) row[i * kSkipWords + w] = s.v[w];
+    if (i == 0) row[kSkipBits * kSkipWords] = s.d;
+}
+
+// Whole warp; the result is valid in lane 0.
+__device__ __forceinline__ float draw_with_table(int seed, int b, const uint32_t* __restrict__ tab)
+{
+    const uint32_t* row = tab + (size_t)b * kSkipRowWords;
+    const int lane = threadIdx.x & 31;
+    curandStateXORWOW_t s;
+    uint32_t v[kSkipWords] = {0u, 0u, 0u, 0u, 0u};
+    if (lane == 0) {
+        curand_init((unsigned long long)seed, 0ULL, 0ULL, &s);
+#pragma unroll
+        for (int w = 0; w < kSkipWords; w++) v[w] = s.v[w];
+    }
+#pragma unroll
+    for (int w = 0; w < kSkipWords; w++) v[w] = __shfl_sync(0xffffffffu, v[w], 0);
+    uint32_t acc[kSkipWords] = {0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int q = 0; q < kSkipBits / 32; q++) {
+        const int bit = q * 32 + lane;  // word q, bit `lane`
+        if ((v[q] >> lane) & 1u) {
+            const uint32_t* col = row + bit * kSkipWords;
+#pragma unroll
+            for (int w = 0; w < kSkipWords; w++) acc[w] ^= col[w];
+        }
+    }
+#pragma unroll
+    for (int w = 0; w < kSkipWords; w++) acc[w] = __reduce_xor_sync(0xffffffffu, acc[w]);
+    float u = 0.f;
+    if (lane == 0) {
+#pragma unroll
+        for (int w = 0; w < kSkipWords; w++) s.v[w] = acc[w];
+        s.d += row[kSkipBits * kSkipWords];
+        u = curand_uniform(&s);
+    }
+    return u;
+}
+
+__global__ void skip_table_check_kernel(const uint32_t* __restrict__ tab, int* __restrict__ mismatches)
+{
+    const int b = blockIdx.x;
+    const int seeds[6] = {0, 1, 2, 515, 12345, 0x7fffffff};
+    for (int i = 0; i < 6; i++) {
+        const float fast = draw_with_table(seeds[i], b, tab);
+        if (threadIdx.x == 0) {
+            curandState_t state;
+            curand_init((unsigned long long)seeds[i], (unsigned long long)b, 0ULL, &state);
+            if (curand_uniform(&state) != fast) atomicAdd(mismatches, 1);
+        }
+    }
+}
+
 __global__ void sample_kernel(const int* __restrict__ topk_id, const float* __restrict__ topk_val, int K,
                               float temperature, int rng_step, const int* __restrict__ rng_step_dev,
                               int vocab_size, int end_id, int literal_walk, int* __restrict__ output_id, int* __restrict__ seqlen,
                               unsigned char* __restrict__ finished, float* __restrict__ u_out,
-                              int* __restrict__ output_id2, int early_seed)
+                              int* __restrict__ output_id2, int early_seed, const uint32_t* __restrict__ skip_tab)
 {
     pdl_launch_dependents();
     const int b = blockIdx.x;
@@ -343,16 +452,20 @@ __global__ void sample_kernel(const int* __restrict__ topk_id, const float* __re
     // counter is advanced by the first kernel of a step, and the layer projections between it and this
     // kernel release their dependents only after passing their own griddepcontrol.wait).
     float u = 0.f;
-    auto draw = [&]() {
-        curandState_t state;
+    auto draw = [&]() {  // whole warp (blockDim.x == 32); u is valid in thread 0
         const int seed = rng_step_dev ? *rng_step_dev : rng_step;
-        curand_init((unsigned long long)seed, (unsigned long long)b, 0ULL, &state);
-        u = curand_uniform(&state);
+        if (skip_tab) {
+            u = draw_with_table(seed, b, skip_tab);
+        } else if (threadIdx.x == 0) {
+            curandState_t state;
+            curand_init((unsigned long long)seed, (unsigned long long)b, 0ULL, &state);
+            u = curand_uniform(&state);
+        }
     };
-    if (early_seed && threadIdx.x == 0) draw();
+    if (early_seed) draw();
     pdl_wait();
-    if (threadIdx.x != 0) return;
     if (!early_seed) draw();
+    if (threadIdx.x != 0) return;
     const float* v = topk_val + (size_t)b * K;
     const float v0 = v[0];
     float sum = 0.f;
@@ -408,7 +521,7 @@ namespace onellm {
 int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, float temperature, int rng_step,
                        const int* rng_step_dev, int vocab_size, int end_id, int literal_walk, int* output_id,
                        int* seqlen, unsigned char* finished, float* u_out, int* output_id2, bool early_seed,
-                       cudaStream_t st)
+                       const uint32_t* skip_table, cudaStream_t st)
 {
     ONELLM_REQUIRE(topk_id && topk_val && output_id, ONELLM_ERR_ARG, "topk_sample: null pointer");
     ONELLM_REQUIRE(B >= 0 && K >= 1 && vocab_size > 0 && temperature > 0.f, ONELLM_ERR_ARG,
@@ -418,7 +531,33 @@ int topk_sample_launch(const int* topk_id, const float* topk_val, int B, int K, 
     if (B == 0) return ONELLM_OK;
     ONELLM_CUDA(launch_pdl(sample_kernel, dim3(B), dim3(32), 0, st, topk_id, topk_val, K, temperature, rng_step,
                            rng_step_dev, vocab_size, end_id, literal_walk, output_id, seqlen, finished, u_out,
-                           output_id2, early_seed ? 1 : 0));
+                           output_id2, early_seed ? 1 : 0, skip_table));
+    return ONELLM_OK;
+}
+
+// Words a skip table for `rows` rows takes.
+size_t skip_table_words(int rows) { return (size_t)rows * kSkipRowWords; }
+
+// Fills `table` (device memory, skip_table_words(rows) words) for rows 0..rows-1 and checks it against the direct
+// draw; waits for the stream.  *usable = 0 when a draw differed (the caller then passes no table).  A table built
+// for `rows` rows serves launches of up to that many rows.
+int build_skip_table(uint32_t* table, int rows, int* usable, cudaStream_t st)
+{
+    ONELLM_REQUIRE(table && usable && rows > 0, ONELLM_ERR_ARG, "skip table: bad argument");
+    int* d_bad = nullptr;
+    ONELLM_CUDA(cudaMalloc(&d_bad, sizeof(int)));
+    cudaError_t e = cudaMemsetAsync(d_bad, 0, sizeof(int), st);
+    if (e == cudaSuccess) {
+        skip_table_kernel<<<rows, kSkipBits, 0, st>>>(table);
+        skip_table_check_kernel<<<rows, 32, 0, st>>>(table, d_bad);
+        e = cudaGetLastError();
+    }
+    int bad = 1;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&bad, d_bad, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_bad);
+    ONELLM_CUDA(e);
+    *usable = bad == 0 ? 1 : 0;
     return ONELLM_OK;
 }
 }  // namespace onellm
@@ -430,5 +569,5 @@ extern "C" int onellm_topk_sample(const int* topk_id, const float* topk_val, int
 {
     return topk_sample_launch(topk_id, topk_val, B, K, temperature, rng_step, rng_step_dev, vocab_size, end_id,
                               literal_walk, output_id, seqlen, finished, u_out, nullptr, /*early_seed=*/false,
-                              reinterpret_cast<cudaStream_t>(stream));
+                              /*skip_table=*/nullptr, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -358,6 +358,27 @@ def test_topk_special_values(ob, cuda, orc, dt):
     assert ri[0].tolist() == list(range(K)) and ri[2, 0] == 7
 
 
+@pytest.mark.parametrize("dt", ["f16", "f32"])
+@pytest.mark.parametrize("copies", [40, 300, 513, 3000])
+def test_topk_runs_of_equal_keys_on_both_ways_through_the_kernel(ob, cuda, orc, dt, copies):
+    """`copies` columns share the row's K-th largest value: up to 512 gathered keys the kernel ranks them directly, beyond
+    that it bisects over all keys; both must give the lowest columns among the equals."""
+    torch = cuda
+    V, K = 32000, 50
+    rng = np.random.default_rng(copies)
+    x = _round(rng.standard_normal((3, V)), dt)
+    for r in range(3):
+        cols = rng.choice(V, copies, replace=False)
+        x[r, cols] = 3.0 + r                       # above nearly everything else
+        x[r, rng.choice(V, 10, replace=False)] = 9.0  # ten columns above the run
+    val = torch.zeros(3, K, device="cuda")
+    idx = torch.zeros(3, K, device="cuda", dtype=torch.int32)
+    ob.topk(ob.F16 if dt == "f16" else ob.F32, _dev(torch, x, dt), 3, V, K, val, idx)
+    rv, ri = orc.topk(x, K)
+    assert np.array_equal(idx.cpu().numpy(), ri)
+    assert np.array_equal(val.cpu().numpy(), rv)
+
+
 def test_topk_reference_case(ob, cuda):
     # tests/unittests/test_beamsearch_topK.cu:12-25: probs[i] = i, V = 30000, K = 2, ids are row*V + column
     torch = cuda

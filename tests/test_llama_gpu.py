@@ -71,6 +71,34 @@ def test_topk_sampling_in_the_loop(ob, cuda, orc, tmp_path):
     m.close()
 
 
+def test_engine_draws_are_the_direct_generator_draws_and_the_sampled_ids_follow(ob, cuda, orc, tmp_path):
+    """The engine takes curand_init's skip-ahead from a table: its draws are bit-equal to the direct call's for the same
+    (step, row), and the ids it samples are the oracle's walk over the engine's own logits with those draws."""
+    import torch
+    m, w = _make(ob, tmp_path, CFG)
+    B, K, T, V = 8, 50, 0.8, CFG["vocab_size"]
+    m.set_sampling(top_k=K, temperature=T)
+    prompt = np.random.default_rng(2).integers(0, V, (B, 5)).astype(np.int32)
+    m.prefill(prompt)
+    out = np.zeros(B, np.int32)
+    for _ in range(4):
+        m.decode_step(None, out)
+        u, step, used = m.last_draws()
+        assert used, "the skip-ahead table did not pass its check against curand_init"
+        idx = torch.zeros(B, K, dtype=torch.int32, device="cuda")
+        val = torch.zeros(B, K, dtype=torch.float32, device="cuda")
+        scratch = torch.zeros(B, dtype=torch.int32, device="cuda")
+        u2 = torch.zeros(B, dtype=torch.float32, device="cuda")
+        ob.topk_sample(idx, val, B, K, T, step, V, 2, scratch, u_out=u2)
+        torch.cuda.synchronize()
+        assert np.array_equal(u[:B], u2.cpu().numpy())
+        tv, ti = orc.topk(m.logits(B), K)
+        want = orc.topk_sample(ti, tv, u[:B], vocab_size=V, end_id=2, temperature=T)
+        want = want[0] if isinstance(want, tuple) else want
+        assert np.array_equal(out, np.asarray(want).reshape(-1)[:B])
+    m.close()
+
+
 def test_loader_errors(ob, cuda, tmp_path):
     m = ob.Llama(**CFG)
     with pytest.raises(ob.OnellmError) as e:
