@@ -109,6 +109,23 @@ ONELLM_API int onellm_decode_attn_ragged(int dtype, const void* q, const void* k
                                          float rope_base, float scale, void* out, long out_stride_b,
                                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* onellm_decode_attn_ragged with the split-KV partials merged inside the attention kernel: one launch whatever
+ * the plan (the other entry points launch a small merge kernel behind a split launch).  tickets: B * H ints of
+ * device memory, zero before the first call; every call leaves them zero.  The last block of a (sequence, head
+ * group) to finish merges the partials of all its splits; no block waits for another.  Same plan, bit-identical
+ * results.  Measured on B200 it is no faster than the two-launch form (slower once a split launch runs several
+ * waves of blocks: every block ends with a fence and an atomic), so onellm_llama_* does not use it; it is here
+ * for hosts where a kernel launch costs more.  Calls that share a ticket array or a workspace must not overlap
+ * on the GPU. */
+ONELLM_API int onellm_decode_attn_merged(int dtype, const void* q, const void* k, const void* v,
+                                         long q_stride_b, long k_stride_b, long v_stride_b,
+                                         const void* bias_q, const void* bias_k, const void* bias_v,
+                                         void* k_cache, void* v_cache, long cs_b, long cs_h, long cs_s,
+                                         int B, int H, int Hkv, int D, int step, const int* step_dev,
+                                         const int* step_offset, int rope_pos, int rot_dim,
+                                         float rope_base, float scale, void* out, long out_stride_b,
+                                         void* workspace, size_t workspace_bytes, int* tickets, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * onellm_decode_attn for callers that cannot allocate device memory.
  * No counterpart in the reference (its layers allocate scratch through BaseAllocator).

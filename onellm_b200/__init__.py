@@ -102,6 +102,24 @@ def decode_attn_ragged(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_
         C.c_long(out_stride_b), _p(workspace), C.c_size_t(workspace_bytes), _stream(stream)))
 
 
+def decode_attn_merged(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache,
+                       cs_b, cs_h, cs_s, B, H, Hkv, D, step, step_offset, rope_pos, rot_dim, rope_base, scale, out,
+                       out_stride_b, workspace, workspace_bytes, tickets, step_dev=None, stream=None):
+    """decode_attn_ragged in one launch: the last block of each (sequence, head group) merges the splits.
+    `tickets`: device int [B * H], zero before the first call (every call leaves it zero)."""
+    _check(lib().onellm_decode_attn_merged(
+        C.c_int(dtype), _p(q), _p(k), _p(v), C.c_long(q_stride_b), C.c_long(k_stride_b), C.c_long(v_stride_b),
+        _p(bias_q), _p(bias_k), _p(bias_v), _p(k_cache), _p(v_cache), C.c_long(cs_b), C.c_long(cs_h),
+        C.c_long(cs_s), C.c_int(B), C.c_int(H), C.c_int(Hkv), C.c_int(D), C.c_int(step), _p(step_dev),
+        _p(step_offset), C.c_int(rope_pos), C.c_int(rot_dim), C.c_float(rope_base), C.c_float(scale), _p(out),
+        C.c_long(out_stride_b), _p(workspace), C.c_size_t(workspace_bytes), _p(tickets), _stream(stream)))
+
+
+def decode_attn_plan_override(blocks_per_sm=0, splits=0):
+    """Tuning aid: fixes the tensor-core decode attention's blocks per SM (1..3) and split count (1..16); 0 = planner."""
+    _check(lib().onellm_decode_attn_plan_override(C.c_int(blocks_per_sm), C.c_int(splits)))
+
+
 def decode_attn_static(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache,
                        cs_b, cs_h, cs_s, B, H, Hkv, D, step, rope_pos, rot_dim, rope_base, scale, out, out_stride_b,
                        step_dev=None, stream=None):

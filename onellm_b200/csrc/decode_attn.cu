@@ -48,6 +48,8 @@ struct DecodeAttnParams {
     long out_sb;
     float* part_acc;  // [B, H, n_split, D]
     float* part_ml;   // [B, H, n_split, 2]
+    int* tickets;     // optional [B, H / G], zero between launches: the last block of a (sequence, head group) to
+                      // arrive merges the splits itself and no merge kernel follows
     int n_split;      // grid.x
     int chunk;        // rows per split
     int nst;          // depth of the shared-memory ring
@@ -58,6 +60,42 @@ __device__ __forceinline__ int effective_splits(int n_cached, int chunk)
 {
     const int s = (n_cached + chunk - 1) / chunk;
     return s < 1 ? 1 : s;
+}
+
+// Split launches without a merge kernel.  Every block of a (sequence, head group) takes a ticket once its partials
+// are written and fenced; the one that draws the last ticket knows that all the others' partials are visible, merges
+// them (the arithmetic of decode_attn_combine_kernel, operation for operation: the results are bit-identical) and
+// puts the ticket counter back to zero for the next launch.  Nobody waits for anybody.  The partials are read
+// past L1 (ld.cg): the same addresses held an earlier launch's partials.  Called by all threads of the block.
+template <typename T>
+__device__ __forceinline__ void merge_by_last_block(const DecodeAttnParams& p, int b, int h0, int G, int n_split)
+{
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* t = p.tickets + (size_t)b * gridDim.y + blockIdx.y;
+        const int last = atomicAdd(t, 1) == n_split - 1;
+        if (last) atomicExch(t, 0);
+        s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * p.D; idx += blockDim.x) {
+        const int h = h0 + idx / p.D, d = idx % p.D;
+        const long base = ((long)b * p.H + h) * p.n_split;
+        float M = -INFINITY;
+        for (int i = 0; i < n_split; i++) M = fmaxf(M, __ldcg(&p.part_ml[(base + i) * 2]));
+        float L = 0.f;
+        for (int i = 0; i < n_split; i++)
+            L = fmaf(__ldcg(&p.part_ml[(base + i) * 2 + 1]), fast_exp2(__ldcg(&p.part_ml[(base + i) * 2]) - M), L);
+        const float invL = 1.f / L;
+        float O = 0.f;
+        for (int i = 0; i < n_split; i++)
+            O = fmaf(__ldcg(&p.part_acc[(base + i) * p.D + d]), fast_exp2(__ldcg(&p.part_ml[(base + i) * 2]) - M), O);
+        reinterpret_cast<T*>(p.out)[b * p.out_sb + (long)h * p.D + d] = (T)(O * invL);
+    }
 }
 
 template <typename T, int LPR, int G>
@@ -331,6 +369,7 @@ __global__ void __launch_bounds__(kAttnThreads) decode_attn_kernel(const DecodeA
             }
         }
     }
+    if (n_split > 1 && p.tickets) merge_by_last_block<T>(p, b, h0, G, n_split);
 }
 
 // Merges the per-split partials: out = sum_i O_i 2^(m_i - M) / sum_i L_i 2^(m_i - M).
@@ -632,6 +671,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32) decode_attn_mma_kernel(const D
             }
         }
     }
+    if (n_split > 1 && p.tickets) merge_by_last_block<__half>(p, b, h0, G, n_split);
 }
 
 constexpr int kMaxSplits = 32;
@@ -731,7 +771,9 @@ static AttnPlan plan_attention_mma(int B, int n_head_blocks, int step, int D, in
     AttnPlan best = {1, rows_all, 2, 2 * kMmaWarps * tile};
     double best_t = 1.0e300;
     const double bytes = 2.0 * (double)n_cached * (double)base * D * 2.0;
-    constexpr double kPeak = 6.5e12, kLatency = 2.3e-6, kWaveCost = 1.0e-6, kMergeCost = 6.0e-6;  // the merge kernel costs a launch boundary in a step, not only its run time
+    // the merge kernel costs a launch boundary in a step, not only its run time (merging inside the attention kernel,
+    // onellm_decode_attn_merged, measured no cheaper: every block then ends with a fence and a ticket)
+    constexpr double kPeak = 6.5e12, kLatency = 2.3e-6, kWaveCost = 1.0e-6, kMergeCost = 6.0e-6;
     const double t_tile = 0.9e-6 * (double)D / 128.0;
     // Two blocks per SM (three stages per warp at D = 128) won or tied every sweep over (blocks per SM, splits) on B200,
     // from 32 to 2560 (sequence, head) pairs and 520 to 2040 rows: three blocks leave one tile in flight per warp, one
@@ -865,7 +907,7 @@ static int decode_attn_impl(int dtype, const void* q, const void* k, const void*
                             void* v_cache, long cs_b, long cs_h, long cs_s, int B, int H, int Hkv, int D, int step,
                             const int* step_dev, const int* step_offset, int rope_pos, int rot_dim, float rope_base,
                             float scale, void* out, long out_stride_b, void* workspace, size_t workspace_bytes,
-                            void* stream)
+                            int* tickets, void* stream)
 {
     ONELLM_REQUIRE(q && k && v && k_cache && v_cache && out, ONELLM_ERR_ARG, "decode_attn: null pointer");
     ONELLM_REQUIRE(B > 0 && H > 0 && Hkv > 0 && D > 0 && step > 0, ONELLM_ERR_ARG,
@@ -933,6 +975,7 @@ static int decode_attn_impl(int dtype, const void* q, const void* k, const void*
                    plan.n_split, step);
     p.part_acc = nullptr;
     p.part_ml = nullptr;
+    p.tickets = tickets;
     if (p.n_split > 1) {
         const size_t need_acc = (size_t)B * H * p.n_split * D * sizeof(float);
         const size_t need = need_acc + (size_t)B * H * p.n_split * 2 * sizeof(float);
@@ -945,7 +988,7 @@ static int decode_attn_impl(int dtype, const void* q, const void* k, const void*
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     ONELLM_CUDA(launch_pdl(kern, dim3(p.n_split, H / G, B), dim3(kAttnThreads), plan.dyn_smem, st, p));
-    if (p.n_split > 1) {
+    if (p.n_split > 1 && !tickets) {
         if (dtype == ONELLM_F16)
             ONELLM_CUDA(launch_pdl(decode_attn_combine_kernel<__half>, dim3(H, B), dim3(128), 0, st, p));
         else
@@ -965,7 +1008,7 @@ extern "C" int onellm_decode_attn(int dtype, const void* q, const void* k, const
 {
     return decode_attn_impl(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache, cs_b,
                             cs_h, cs_s, B, H, Hkv, D, step, step_dev, nullptr, rope_pos, rot_dim, rope_base, scale, out,
-                            out_stride_b, workspace, workspace_bytes, stream);
+                            out_stride_b, workspace, workspace_bytes, nullptr, stream);
 }
 
 // Sequences of different lengths in one batch: sequence b attends step + step_offset[b] rows (the new one included),
@@ -980,7 +1023,28 @@ extern "C" int onellm_decode_attn_ragged(int dtype, const void* q, const void* k
 {
     return decode_attn_impl(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache, cs_b,
                             cs_h, cs_s, B, H, Hkv, D, step, step_dev, step_offset, rope_pos, rot_dim, rope_base, scale, out,
-                            out_stride_b, workspace, workspace_bytes, stream);
+                            out_stride_b, workspace, workspace_bytes, nullptr, stream);
+}
+
+// The same call with the splits merged inside the attention kernel (one launch whatever the plan): `tickets` is
+// B * H ints of device memory that are zero before the first call; every call leaves them zero.  Calls that share a
+// ticket array must not overlap on the GPU.  Same plan and same bits as the two-launch form.  On B200 it measured
+// SLOWER than the two-launch form wherever a plan splits (inside a decoder layer 1.5-4 us at the 7B shape over 2-8
+// GPUs, 7-11 us at the 13B shape, batch 64: every block of a split launch ends with a fence, a barrier and an
+// atomic, which costs more over several waves of blocks than one small merge launch), so the model class keeps the
+// two-launch form; the entry point stays for hosts where a launch is dearer than that.
+extern "C" int onellm_decode_attn_merged(int dtype, const void* q, const void* k, const void* v, long q_stride_b,
+                                         long k_stride_b, long v_stride_b, const void* bias_q, const void* bias_k,
+                                         const void* bias_v, void* k_cache, void* v_cache, long cs_b, long cs_h,
+                                         long cs_s, int B, int H, int Hkv, int D, int step, const int* step_dev,
+                                         const int* step_offset, int rope_pos, int rot_dim, float rope_base,
+                                         float scale, void* out, long out_stride_b, void* workspace,
+                                         size_t workspace_bytes, int* tickets, void* stream)
+{
+    ONELLM_REQUIRE(tickets, ONELLM_ERR_ARG, "decode_attn_merged: null ticket array");
+    return decode_attn_impl(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_q, bias_k, bias_v, k_cache, v_cache, cs_b,
+                            cs_h, cs_s, B, H, Hkv, D, step, step_dev, step_offset, rope_pos, rot_dim, rope_base, scale, out,
+                            out_stride_b, workspace, workspace_bytes, tickets, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

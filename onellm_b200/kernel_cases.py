@@ -121,11 +121,16 @@ def make_case(name, torch, model="7b", batch=8, ctx=2040, tp=1, plain=False) -> 
         wsb = ob.decode_attn_workspace_bytes(B, H, D, S)
         ws = torch.empty(wsb, device="cuda", dtype=torch.uint8)
         p, step = qkv.data_ptr(), ctx + 1
+        tickets = torch.zeros(B * H, device="cuda", dtype=torch.int32)
         fn = lambda i: ob.decode_attn(F16, p, p + H * D * 2, p + 2 * H * D * 2, 3 * H * D, 3 * H * D, 3 * H * D, None, None, None,
                                       kc[i], vc[i], H * S * D, S * D, D, B, H, H, D, step, step - 1, D, 10000.0, D ** -0.5, o,
                                       H * D, ws, wsb)
+        if plain:  # the one-launch form (splits merged by the last block), which the model class does not use
+            fn = lambda i: ob.decode_attn_merged(F16, p, p + H * D * 2, p + 2 * H * D * 2, 3 * H * D, 3 * H * D, 3 * H * D, None,
+                                                 None, None, kc[i], vc[i], H * S * D, S * D, D, B, H, H, D, step, None, step - 1, D,
+                                                 10000.0, D ** -0.5, o, H * D, ws, wsb, tickets)
         return Case(fn, rot, 2 * ctx * B * H * D * 2 + 5 * B * H * D * 2, "B", "decode_attn_mma_kernel<128,1>",
-                    keep=(kc, vc, qkv, o, ws))
+                    keep=(kc, vc, qkv, o, ws, tickets))
     if name == "attn_c1":
         # the reference's unit-test shape in fp32: 16.9 MB per launch, far below L2 -> rotate over > 126 MB of caches
         Bc, Hc, Dc, Sc, step = 2, 32, 128, 256, 255
@@ -298,7 +303,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=None, help="cache rows (decode cases, default 2040) / new tokens per sequence (prefill cases, default 512)")
     ap.add_argument("--graph", action="store_true", help="time a CUDA graph of the launches (device-side back-to-back)")
     ap.add_argument("--tp", type=int, default=1, help="per-rank shapes of a tensor-parallel degree (heads and FFN columns divided)")
-    ap.add_argument("--plain", action="store_true", help="projections through onellm_gemm / onellm_gemm_swiglu instead of onellm_gemm_fused")
+    ap.add_argument("--plain", action="store_true", help="projections through onellm_gemm / onellm_gemm_swiglu instead of onellm_gemm_fused; attn: onellm_decode_attn_merged (splits merged inside the kernel) instead of onellm_decode_attn")
     a = ap.parse_args()
     ctx = a.ctx if a.ctx is not None else (512 if a.case.startswith("prefill_") else 2040)
     torch.cuda.set_device(0)

@@ -155,6 +155,55 @@ def test_decode_attn_ragged_batch(ob, cuda, orc, dt, H, Hkv, D, steps, S):
     assert rel_err(d_vc.float().cpu().numpy(), vc_ref) < TOL[dt]
 
 
+@pytest.mark.parametrize("dt,H,Hkv,D,steps,S,splits", [
+    ("f16", 8, 8, 128, (700, 300, 65), 1024, 5), ("f16", 8, 2, 64, (900, 899), 1024, 8), ("f16", 4, 4, 128, (2000,), 2048, 16),
+    ("f16", 32, 32, 128, (520, 520, 519, 2), 1024, 0), ("f32", 4, 4, 128, (500, 130, 1), 512, 0)])
+def test_decode_attn_merged_in_the_kernel_equals_the_two_launch_form(ob, cuda, orc, dt, H, Hkv, D, steps, S, splits):
+    """Split launches merged by the last block of each (sequence, head group) give the bits the separate merge kernel
+    gives for the same plan, leave the ticket array zero (a second call on it gives the same bits), and match the oracle."""
+    torch = cuda
+    B = len(steps)
+    rng = np.random.default_rng(S + B)
+    u = lambda *s: _round(rng.uniform(-1, 1, s), dt)
+    qkv, kc, vc = u(B, H + 2 * Hkv, D), u(B, Hkv, S, D), u(B, Hkv, S, D)
+    for b, st in enumerate(steps):
+        kc[b, :, st - 1:], vc[b, :, st - 1:] = 0, 0
+    refs = []
+    for b, st in enumerate(steps):
+        kb, vb = np.ascontiguousarray(kc[b:b + 1]).copy(), np.ascontiguousarray(vc[b:b + 1]).copy()
+        refs.append(orc.decode_attn(qkv[b:b + 1, :H], qkv[b:b + 1, H:H + Hkv], qkv[b:b + 1, H + Hkv:], kb, vb, st, rope_pos=st - 1))
+    ref = np.concatenate(refs)
+    longest = max(steps)
+    d_qkv = _dev(torch, qkv, dt)
+    off = torch.tensor([st - longest for st in steps], device="cuda", dtype=torch.int32)
+    step_dev = torch.tensor([longest], device="cuda", dtype=torch.int32)
+    wsb = ob.decode_attn_workspace_bytes(B, H, D, S)
+    esz, base, ld = d_qkv.element_size(), d_qkv.data_ptr(), (H + 2 * Hkv) * D
+    code = ob.F16 if dt == "f16" else ob.F32
+    tickets = torch.zeros(B * H, device="cuda", dtype=torch.int32)
+    outs = []
+    try:
+        ob.decode_attn_plan_override(0, splits)
+        for form in ("two launches", "merged", "merged again"):
+            d_kc, d_vc = _dev(torch, kc, dt), _dev(torch, vc, dt)
+            ws = torch.full((wsb,), 0x7f, device="cuda", dtype=torch.uint8)  # stale partials must not matter
+            out = torch.zeros(B, H, D, device="cuda", dtype=_dt(torch, dt))
+            args = (code, base, base + H * D * esz, base + (H + Hkv) * D * esz, ld, ld, ld, None, None, None, d_kc, d_vc,
+                    Hkv * S * D, S * D, D, B, H, Hkv, D, S, off, S - 1, D, 10000.0, 1.0 / np.sqrt(D), out, H * D, ws, wsb)
+            if form == "two launches":
+                ob.decode_attn_ragged(*args, step_dev=step_dev)
+            else:
+                ob.decode_attn_merged(*args, tickets, step_dev=step_dev)
+            torch.cuda.synchronize()
+            outs.append(out.float().cpu().numpy())
+            assert int(tickets.abs().sum().item()) == 0
+    finally:
+        ob.decode_attn_plan_override(0, 0)
+    assert rel_err(outs[0], ref) < TOL[dt]
+    assert np.array_equal(outs[0], outs[1])  # the same plan in both forms
+    assert np.array_equal(outs[1], outs[2])
+
+
 def test_decode_attn_partial_rotary(ob, cuda, orc):
     got, ref, *_ = _run_decode_attn(ob, cuda, orc, "f32", 2, 4, 4, 128, 40, 64, "bhsd", 5, rot_dim=64)
     assert rel_err(got, ref) < TOL["f32"]
