@@ -528,13 +528,35 @@ static StagedPlan plan_for(bool dual, int N, int K)
 }
 
 // The plan a projection of M tokens would be launched with (K split, ring depth, thread blocks).
+bool skinny_tc_takes(int M, int N, int K);                                      // skinny_gemm_tc.cu
+cudaError_t skinny_tc_plan_query(int N, int K, bool dual, int* ks, int* nst);  // skinny_gemm_tc.cu
+
 cudaError_t staged_plan_query(int M, int N, int K, bool dual, int* ks, int* nst, int* blocks)
 {
+    if (skinny_tc_takes(M, N, K)) {
+        int k = 1, n = 3;
+        const cudaError_t e = skinny_tc_plan_query(N, K, dual, &k, &n);
+        if (ks) *ks = k;
+        if (nst) *nst = n;
+        if (blocks) *blocks = k * ((N + kBN - 1) / kBN);
+        return e;
+    }
     const StagedPlan p = M <= 8 ? plan_for<1>(dual, N, K) : M <= 16 ? plan_for<2>(dual, N, K) : M <= 32 ? plan_for<4>(dual, N, K) : plan_for<8>(dual, N, K);
     if (ks) *ks = p.ks;
     if (nst) *nst = p.nst;
     if (blocks) *blocks = p.ks * ((N + kBN - 1) / kBN);
     return p.status;
+}
+
+// The override registered for a shape, if any (also honoured by the tcgen05 kernel's planner).
+bool plan_override_lookup(int N, int K, bool dual, int* ks, int* nst)
+{
+    std::lock_guard<std::mutex> lock(g_override_mu);
+    auto ov = plan_overrides().find(std::make_tuple(N, K, dual));
+    if (ov == plan_overrides().end()) return false;
+    *ks = ov->second.first;
+    *nst = ov->second.second;
+    return true;
 }
 
 void staged_plan_override(int N, int K, bool dual, int ks, int nst)

@@ -212,6 +212,8 @@ struct TcPlan {
     cudaError_t status;
 };
 
+bool plan_override_lookup(int N, int K, bool dual, int* ks, int* nst);  // skinny_gemm_staged.cu (onellm_gemm_plan_override)
+
 static int g_tc_min_tokens = 33;  // projections of at least this many tokens take this kernel (onellm_gemm_tc_min_tokens)
 
 template <bool DUAL>
@@ -225,16 +227,92 @@ static TcPlan plan_tc(int N, int K, bool tp)
     constexpr int max_nst = (int)((cap - 1024 - kSkBarBytes) / stage);  // 9 (5 with two weights)
     static DeviceOnce attr;
     TcPlan plan = {1, 3, 0, 0, cudaSuccess};
-    plan.status = attr.run([kern] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap); });
+    // the shared-memory carve-out preference comes first: the occupancy queries below answer for the carve-out the
+    // kernel currently asks for, and with the default one they see a single block per SM whatever the ring depth
+    plan.status = attr.run([kern] {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap);
+        return e != cudaSuccess ? e : prefer_max_shared((const void*)kern);
+    });
     if (plan.status != cudaSuccess) return plan;
+    const int col_tiles = (N + kBN - 1) / kBN;
+    const int total_stages = (K + kSkBK - 1) / kSkBK;
+    int oks = 0, onst = 0;
+    if (!tp && plan_override_lookup(N, K, DUAL, &oks, &onst)) {  // tuning aid; never cached
+        const int per = oks >= 1 ? (total_stages + oks - 1) / oks : 0;
+        if (oks < 1 || oks > 8 || oks > total_stages || per * (oks - 1) >= total_stages || onst < 2 || onst > max_nst) {
+            plan.status = cudaErrorInvalidValue;
+            return plan;
+        }
+        plan.ks = oks;
+        plan.per_block = per;
+        plan.nst = onst;
+        plan.smem = std::max(stage * onst, red) + 1024 + kSkBarBytes;
+        return plan;
+    }
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     static std::map<std::tuple<int, int, bool, int>, TcPlan> plans;
     const auto key = std::make_tuple(N, K, tp, current_device());
     auto it = plans.find(key);
     if (it != plans.end()) return it->second;
-    const int col_tiles = (N + kBN - 1) / kBN;
-    const int total_stages = (K + kSkBK - 1) / kSkBK;
+    // How many clusters of `ks` blocks with an `nst`-stage ring the GPU holds at once (the runtime's answer).
+    auto resident_clusters = [&](int ks, int nst) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 1;
+        at[0].val.clusterDim.y = ks;
+        at[0].val.clusterDim.z = 1;
+        cfg.gridDim = dim3(col_tiles, ks, 1);
+        cfg.blockDim = dim3(kSkThreads);
+        cfg.dynamicSmemBytes = std::max(stage * nst, red) + 1024 + kSkBarBytes;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        const cudaError_t oe = cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg);
+        if (oe != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        // The occupancy calculators answer one block per SM for this kernel whatever its shared memory, registers
+        // (53-64) and threads would allow: they cannot know how much tensor memory a block allocates at run time.
+        // A block takes 64 or 128 of the 512 columns, so two blocks share an SM when their rings fit (what the
+        // timings show: the 250-tile LM head runs as one wave with a four-stage ring).  The runtime's figure for the
+        // cluster size (which knows how clusters pack into GPCs) is scaled by that.
+        const size_t per_block = cfg.dynamicSmemBytes + 2048;  // + static and system-reserved shared memory
+        const int by_smem = (int)((size_t)228 * 1024 / per_block);
+        const int per_sm = std::min(2, std::max(1, by_smem));
+        return clusters * per_sm;
+    };
+    auto take = [&](int ks, int nst) {
+        plan.ks = ks;
+        plan.per_block = (total_stages + ks - 1) / ks;
+        plan.nst = nst;
+        plan.smem = std::max(stage * nst, red) + 1024 + kSkBarBytes;
+        if (tp && (long)col_tiles * ks > kTpMaxBlocks) plan.status = cudaErrorInvalidConfiguration;
+        plans[key] = plan;
+        return plan;
+    };
+    // Plans found by the sweep of python -m onellm_b200.tune_plans (one decoder layer as a CUDA graph as the objective)
+    // for the 13B shape split 2, 4 and 8 ways at 33-64 tokens: a ring of 3-6 stages leaves room for two blocks per
+    // SM, which then hide each other's start-up and reduction, and allows a wider K split.  Used when all their
+    // blocks are resident at once (which the tensor-parallel epilogue needs in any case).
+    struct Tuned {
+        int N, K;
+        bool dual;
+        int ks, nst;
+    };
+    static const Tuned kTuned[] = {
+        {7680, 5120, false, 5, 3}, {5120, 2560, false, 5, 4}, {5120, 6912, false, 4, 4},                               // 2 ways
+        {3840, 5120, false, 4, 6}, {5120, 1280, false, 5, 3}, {3456, 5120, true, 4, 4}, {5120, 3456, false, 6, 4},  // 4 ways
+        {1920, 5120, false, 8, 6}, {5120, 640, false, 5, 3},  {1728, 5120, true, 8, 4}, {5120, 1728, false, 4, 4},  // 8 ways
+    };
+    for (const Tuned& t : kTuned) {
+        if (t.N != N || t.K != K || t.dual != DUAL || t.nst > max_nst) continue;
+        const int per = (total_stages + t.ks - 1) / t.ks;
+        if (t.ks > total_stages || per * (t.ks - 1) >= total_stages) continue;
+        if (resident_clusters(t.ks, t.nst) >= col_tiles) return take(t.ks, t.nst);
+    }
     // One block per SM (the ring takes the shared memory): the largest K split, of at least two stages per block,
     // whose blocks are all resident at once; the runtime says how many clusters of that size fit.
     int best_ks = 0;
@@ -266,8 +344,11 @@ static TcPlan plan_tc(int N, int K, bool tp)
         }
     }
     if (best_ks == 0) {
-        // more column tiles than SMs: no K split, several waves (not for the tensor-parallel epilogue, whose blocks wait
-        // for the blocks of the same index on the other GPUs)
+        // More column tiles than SMs (the LM head: 250 tiles).  A four-stage ring lets two blocks share an SM: one wave
+        // instead of 1.7 (13B LM head at 64 tokens: 58.6 us instead of 85.9).
+        if (resident_clusters(1, 4) >= col_tiles) return take(1, 4);
+        // else no K split and several waves (not for the tensor-parallel epilogue, whose blocks wait for the blocks of
+        // the same index on the other GPUs)
         if (tp) plan.status = cudaErrorInvalidConfiguration;
         best_ks = 1;
     }
@@ -308,6 +389,14 @@ static cudaError_t launch_tc(const __half* x, const __half* W0, const __half* W1
     cfg.numAttrs = 2;
     note_launch();
     return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<DUAL>, map_w0, map_w1, map_x, y, M, N, K, plan.per_block, plan.nst, ep);
+}
+
+cudaError_t skinny_tc_plan_query(int N, int K, bool dual, int* ks, int* nst)
+{
+    const TcPlan p = dual ? plan_tc<true>(N, K, false) : plan_tc<false>(N, K, false);
+    *ks = p.ks;
+    *nst = p.nst;
+    return p.status;
 }
 
 // True when a projection of M tokens goes to this kernel rather than to the mma.sync one.

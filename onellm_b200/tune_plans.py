@@ -62,7 +62,7 @@ def main():
     for rnd in range(2):
         for name, (N, K, dual) in shapes.items():
             results = []
-            for ks, nst in itertools.product(range(1, 9), [3, 4, 5, 6, 8, 10, 12]):
+            for ks, nst in itertools.product(range(1, 9), [3, 4, 5, 6, 7, 8, 9, 10, 12]):
                 if ks > 1 and K // 32 // ks < 4:
                     continue
                 ob.gemm_plan_override(N, K, dual, ks, nst)

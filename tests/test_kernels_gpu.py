@@ -565,8 +565,10 @@ def test_gemm_f16_tensor_core_tiles(ob, cuda, orc, M, N, K, nk):
     (1920, 5120, False, True, False),     # 13B QKV, one of eight ranks: 15 column tiles, the K range split eight ways
     (5120, 640, False, False, True),      # 13B o_proj slice: ten 64-row stages in all
     (1728, 5120, True, True, False),      # gate/up slice: the last column tile is half empty
-    (32000, 4096, False, False, False),   # LM head: more column tiles than SMs
+    (32000, 4096, False, False, False),   # LM head: more column tiles than SMs (two blocks per SM, one wave)
     (1000, 528, True, False, True),       # ragged in N and K
+    (5120, 1728, False, False, True),     # 13B down_proj slices: tuned plans with two blocks per SM
+    (5120, 3456, False, False, True),
 ])
 def test_gemm_tensor_core_weight_streaming_kernel(ob, cuda, orc, M, N, K, dual, rms, resid):
     """The tcgen05 kernel for 17..64 tokens (forced from 17 tokens up here) against the oracle, and bit-identical to itself."""
@@ -595,6 +597,44 @@ def test_gemm_tensor_core_weight_streaming_kernel(ob, cuda, orc, M, N, K, dual, 
         assert torch.equal(outs[0], outs[1])
     finally:
         ob.gemm_tc_min_tokens(before)
+
+
+@pytest.mark.parametrize("ks,nst", [(1, 3), (5, 3), (7, 4), (3, 9), (2, 6)])
+def test_gemm_tensor_core_kernel_under_a_forced_plan(ob, cuda, orc, ks, nst):
+    """onellm_gemm_plan_override reaches the tcgen05 kernel too: every (K split, ring depth) gives the oracle's result."""
+    torch = cuda
+    M, N, K = 64, 5120, 1280
+    rng = np.random.default_rng(ks * 16 + nst)
+    x = _round(2.0 * rng.standard_normal((M, K)), "f16")
+    W = _round(0.02 * rng.standard_normal((K, N)), "f16")
+    r = _round(rng.standard_normal((M, N)), "f16")
+    try:
+        ob.gemm_plan_override(N, K, False, ks, nst)
+        assert ob.gemm_plan_query(M, N, K, False)[:2] == (ks, nst)
+        y = _dev(torch, r, "f16")
+        ob.gemm_fused(ob.F16, _dev(torch, x, "f16"), _dev(torch, W, "f16"), None, y, M, N, K, rms_eps=-1.0, resid=y, bias=None)
+        torch.cuda.synchronize()
+        assert ob.lib().onellm_gemm_timeout_flag() == 0
+        assert rel_err(y.float().cpu().numpy(), orc.gemm(x, W) + r) < TOL["f16"]
+    finally:
+        ob.gemm_plan_override(N, K, False, 0, 3)
+    assert ob.gemm_plan_query(M, N, K, False)[:2] == (5, 3)  # the tuned plan of this shape is back
+
+
+def test_gemm_tensor_core_kernel_refuses_a_plan_that_leaves_a_block_without_rows(ob, cuda):
+    torch = cuda
+    M, N, K = 64, 5120, 1280  # twenty 64-row stages: split eight ways, three per block, the eighth block would get none
+    x = torch.zeros(M, K, device="cuda", dtype=torch.float16)
+    W = torch.zeros(K, N, device="cuda", dtype=torch.float16)
+    y = torch.zeros(M, N, device="cuda", dtype=torch.float16)
+    try:
+        ob.gemm_plan_override(N, K, False, 8, 4)
+        with pytest.raises(ob.OnellmError):
+            ob.gemm_fused(ob.F16, x, W, None, y, M, N, K, rms_eps=-1.0, resid=None, bias=None)
+    finally:
+        ob.gemm_plan_override(N, K, False, 0, 3)
+    ob.gemm_fused(ob.F16, x, W, None, y, M, N, K, rms_eps=-1.0, resid=None, bias=None)
+    torch.cuda.synchronize()
 
 
 @pytest.mark.parametrize("M,N,K", [(300, 512, 256), (1024, 4096, 4096), (130, 1000, 528)])
