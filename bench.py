@@ -261,6 +261,7 @@ def run_reference(args, workload):
                                "themselves are timed under cpu_baseline.reference_helpers"},
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc,
                              "spread": spread, "reference_helpers": reference_helper_timings()},
+            "reference_gpu_kernels": reference_gpu_kernel_timings(),
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -311,8 +312,103 @@ def config_cases(torch, hbm_peak, tf_peak):
                                               "the epilogue), RoPE + cache write, causal attention, o_proj + residual, gate/up + SwiGLU, "
                                               "down + residual; attention counted over the full square"}
     del case
+    out.update(fp32_cases(torch, hbm_peak))
     torch.cuda.empty_cache()
     return out
+
+
+def _time_rotating(torch, fn, n_buffers, iters=20, warm=3):
+    """Mean seconds per call of fn(i) over rotating buffers; CUDA events on the current (legacy default) stream."""
+    for i in range(warm):
+        fn(i % n_buffers)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i % n_buffers)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+FP32_SHAPES = {"rmsnorm_f32_4096x4096": (4096, 4096), "swiglu_f32_4096x11008": (4096, 11008),
+               "embedding_f32_4096_ids_32000x4096": (4096, 4096, 32000)}
+
+
+def fp32_cases(torch, hbm_peak):
+    """This library's kernels in fp32 on the shapes the reference arm times the reference's own (fp32-only) CUDA kernels on."""
+    import onellm_b200 as ob
+    out = {}
+    T, Hd = FP32_SHAPES["rmsnorm_f32_4096x4096"]
+    xs = [torch.randn(T, Hd, device="cuda") for _ in range(4)]  # 4 x 67 MB: past the 126 MB L2
+    g = torch.ones(Hd, device="cuda")
+    t = _time_rotating(torch, lambda i: ob.rmsnorm(ob.F32, xs[i], g, 1e-5, T, Hd), 4)
+    nbytes = 2 * T * Hd * 4
+    out["rmsnorm_f32_4096x4096"] = {"kernel": "rmsnorm_kernel<float>", "bytes": nbytes, "us": t * 1e6, "gbs": nbytes / t / 1e9,
+                                    "frac_of_hbm": nbytes / t / 1e9 / hbm_peak}
+    del xs
+    T, I = FP32_SHAPES["swiglu_f32_4096x11008"]
+    ins = [torch.randn(T, 2, I, device="cuda") for _ in range(2)]
+    o = torch.empty(T, I, device="cuda")
+    t = _time_rotating(torch, lambda i: ob.swiglu(ob.F32, ins[i], o, T, I), 2)
+    nbytes = 3 * T * I * 4
+    out["swiglu_f32_4096x11008"] = {"kernel": "swiglu_kernel<float>", "bytes": nbytes, "us": t * 1e6, "gbs": nbytes / t / 1e9,
+                                    "frac_of_hbm": nbytes / t / 1e9 / hbm_peak}
+    del ins, o
+    n, Hd, V = FP32_SHAPES["embedding_f32_4096_ids_32000x4096"]
+    table = torch.randn(V, Hd, device="cuda")
+    ids = [torch.randint(0, V, (n,), device="cuda", dtype=torch.int32) for _ in range(4)]
+    o = [torch.empty(n, Hd, device="cuda") for _ in range(4)]
+    t = _time_rotating(torch, lambda i: ob.embedding(ob.F32, ids[i], o[i], table, n, Hd, V), 4)
+    nbytes = 2 * n * Hd * 4
+    out["embedding_f32_4096_ids_32000x4096"] = {"kernel": "embedding_kernel<float>", "bytes": nbytes, "us": t * 1e6,
+                                                "gbs": nbytes / t / 1e9, "frac_of_hbm": nbytes / t / 1e9 / hbm_peak}
+    return out
+
+
+def reference_gpu_kernel_timings():
+    """The reference's own CUDA kernels (its launch* functions compiled for sm_100a from the reference tree into
+    oracle/_ref/libonellm_ref.so; fp32, the only type its launchers instantiate everywhere), timed with CUDA events on the
+    shapes of fp32_cases.  Each export synchronises the device after its launch; the events bracket the launches only."""
+    try:
+        import torch
+        from oracle import ref_lib
+        lib = ref_lib.load()
+        if lib is None:
+            return {"unavailable": "oracle/_ref/libonellm_ref.so has not been built (needs the reference tree at build time)"}
+        if not torch.cuda.is_available():
+            return {"unavailable": "no GPU"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": str(e)}
+    import ctypes as C
+    p = lambda t: C.c_void_p(t.data_ptr())
+    out = []
+    T, Hd = FP32_SHAPES["rmsnorm_f32_4096x4096"]
+    xs = [torch.randn(T, Hd, device="cuda") for _ in range(4)]
+    g = torch.ones(Hd, device="cuda")
+    t = _time_rotating(torch, lambda i: lib.ref_gpu_rmsnorm(p(xs[i]), p(g), C.c_float(1e-5), T, Hd), 4, iters=10)
+    out.append({"fn": "launchRMSNorm (src/kernels/rmsnorm_kernel.cu)", "case": "rmsnorm_f32_4096x4096", "us": t * 1e6,
+                "gbs": 2 * T * Hd * 4 / t / 1e9})
+    del xs
+    T, I = FP32_SHAPES["swiglu_f32_4096x11008"]
+    ins = [torch.randn(T, 2, I, device="cuda") for _ in range(2)]
+    o = torch.empty(T, I, device="cuda")
+    t = _time_rotating(torch, lambda i: lib.ref_gpu_swiglu(p(ins[i]), p(o), T, I), 2, iters=10)
+    out.append({"fn": "launchAct (src/kernels/activation_kernel.cu)", "case": "swiglu_f32_4096x11008", "us": t * 1e6,
+                "gbs": 3 * T * I * 4 / t / 1e9})
+    del ins, o
+    n, Hd, V = FP32_SHAPES["embedding_f32_4096_ids_32000x4096"]
+    table = torch.randn(V, Hd, device="cuda")
+    ids = [torch.randint(0, V, (8, n // 8), device="cuda", dtype=torch.int32) for _ in range(4)]
+    o = [torch.empty(n, Hd, device="cuda") for _ in range(4)]
+    t = _time_rotating(torch, lambda i: lib.ref_gpu_embedding(p(ids[i]), p(o[i]), p(table), 8, n // 8, Hd, V), 4, iters=10)
+    out.append({"fn": "launchInputEmbedding (src/kernels/input_embedding.cu)", "case": "embedding_f32_4096_ids_32000x4096",
+                "us": t * 1e6, "gbs": 2 * n * Hd * 4 / t / 1e9})
+    out.append({"fn": "launchDecoderMaskedMHA (src/kernels/decoder_masked_attn.cu)",
+                "unavailable": "the kernel is well defined only for step <= head size (its softmax covers the first blockDim "
+                               "logits) and Hkv == H in [S, B, H, D] caches; the bench shapes (step 255-2040) lie outside, so it "
+                               "is not launched there.  Parity inside its range: tests/test_ref_kernels_gpu.py"})
+    return {"kernels": out, "compare_with": "configs.*_f32_* of the line without --impl reference"}
 
 
 def run_ours(args, workload):
