@@ -5,14 +5,12 @@
 // to 1 <= K <= 64 with a defined order for ties (lower column first).  Sampling restates
 // SamplingKernel (src/kernels/topK_sampling.cu:6-41) with the same cuRAND call sequence.
 //
-// Top-K is a radix select, one thread block per row: 8-bit histogram passes over an
-// order-preserving integer image of the logits find the K-th largest key (two passes for fp16
-// logits, whose image has 16 bits, four for fp32), then everything above it plus the
-// lowest-indexed ties are gathered and rank-sorted.  Rows of up to 32768 logits are read once:
-// every thread keeps its 32 consecutive keys in registers for all passes; histogram updates are
-// aggregated per warp before they reach shared memory (logits share their leading bits, so
-// plain atomics would serialise on a handful of bins).  Longer rows re-read the logits from L2
-// in every pass.
+// One thread block per row, over an order-preserving integer image of the logits (NaN lowest).  Rows of up to
+// 32768 logits (topk_reg_kernel) are read once, 32 consecutive keys per thread in registers: the K-th largest of
+// the per-thread maxima bounds the K-th largest key from below, the few keys that reach it are gathered and ranked
+// against each other; rows with long runs of equal keys fall back to a bisection over all keys.  Neither step
+// uses a histogram: logits share their leading bits, and a 256-bin histogram in shared memory serialises on a
+// handful of bins.  Longer rows (topk_kernel) are a radix select, 8 bits per pass, re-reading the logits from L2.
 #include <curand_kernel.h>
 #include <math.h>
 
@@ -179,16 +177,6 @@ __device__ __forceinline__ float key_value<__half>(uint32_t k)
 
 constexpr int kTopkPer = 32;  // keys per thread held in registers
 constexpr int kTopkCand = 512;  // gathered keys the short way ranks; >= kMaxK
-
-// warp-aggregated histogram update: lanes with the same digit elect one to add their count
-__device__ __forceinline__ void hist_add(int* hist, bool pred, uint32_t digit)
-{
-    const unsigned act = __ballot_sync(0xffffffffu, pred);
-    if (pred) {
-        const unsigned peers = __match_any_sync(act, digit);
-        if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[digit], __popc(peers));
-    }
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kTopkThreads)
