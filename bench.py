@@ -424,6 +424,8 @@ def run_ours(args, workload):
     torch.cuda.set_device(local)
     model, batch, prompt_len, smax, top_k, temp = WORKLOADS[workload]
     m = ob.Llama(**model, max_seq_len=smax, max_batch=batch, tp_rank=rank, tp_size=world)
+    if args.two_shot_bytes >= 0:
+        ob.p2p_two_shot_bytes(args.two_shot_bytes)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -587,6 +589,9 @@ def run_ours(args, workload):
                            "top_k": top_k, "temperature": temp, "parallelism": f"tp{world}",
                            "allreduce": ("none" if world == 1 else ("nccl" if args.tp_nccl_only else
                                          "inside the o_proj / down_proj kernels over peer memory (NCCL for the context phase)")),
+                           "two_shot": (bool((world > 2 or ob.p2p_two_shot_bytes() == 0) and
+                                             (world - 1) * batch * model["hidden"] * 4 >= ob.p2p_two_shot_bytes())
+                                        if world > 1 and not args.tp_nccl_only else None),
                            "l2": "every step streams its weights and KV cache (>13 GB) once: inputs exceed the 126 MB L2",
                            "context_during_timing": [start_len, start_len + K],
                            "prefill": "skipped (cache seek, profiling)" if args.skip_prefill else "done before the timed region"},
@@ -647,6 +652,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-cases", action="store_true", help="skip the kernel-level configurations")
     ap.add_argument("--tp-nccl-only", action="store_true", help="N > 1: keep ncclAllReduce in the decode step (comparison)")
+    ap.add_argument("--two-shot-bytes", type=int, default=-1,
+                    help="N > 1: threshold of onellm_p2p_two_shot_bytes (0 = always two-shot, a huge value = never); default: the library's")
     ap.add_argument("--skip-prefill", action="store_true", help="profiling aid: seek to the prompt length instead of prefilling")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel roofline leg")
     args = ap.parse_args()

@@ -435,6 +435,18 @@ ONELLM_API int onellm_p2p_allreduce_add(onellm_p2p* comm, int dtype, int which, 
  * mixed with a concurrent onellm_p2p_allreduce_add on the same `which`. */
 ONELLM_API int onellm_p2p_gemm_allreduce_add(onellm_p2p* comm, int dtype, int which, const void* x, const void* W,
                                              void* resid, const void* bias, int M, int N, int K, void* stream);
+
+/* The exchange inside onellm_p2p_gemm_allreduce_add has two forms with the same arithmetic and the same bits.
+ * One-shot: every rank sends its partial of an element to every peer and adds what it receives (one hop, world - 1
+ * copies of the message per rank on the wire).  Two-shot: token row t belongs to rank t % world; partials go to
+ * the owner only, which adds them, the residual and the bias and sends the finished value to everybody (two hops,
+ * 2 (world - 1) / world of one message per rank).  The two-shot form is taken when the one-shot form would put
+ * at least `bytes` on the wire per rank, (world - 1) * M * N * 4, and there are more than two ranks (default
+ * 3 MiB: the 64-token messages of a 13B model on 4 or 8 ranks, not a batch of 8).  Returns the previous threshold;
+ * a negative argument only reads it; 0 = always two-shot, on two ranks too.  Process-wide; every rank must use the
+ * same value. */
+ONELLM_API long long onellm_p2p_two_shot_bytes(long long bytes);
+
 ONELLM_API int onellm_p2p_error(onellm_p2p* comm);
 ONELLM_API void onellm_p2p_destroy(onellm_p2p* comm);
 

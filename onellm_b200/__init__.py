@@ -284,6 +284,13 @@ def topk_sample(topk_id, topk_val, B, K, temperature, rng_step, vocab_size, end_
                                     _p(u_out), _stream(stream)))
 
 
+def p2p_two_shot_bytes(nbytes=-1):
+    """Threshold (one-shot wire bytes per rank) from which the projections' exchange goes two-shot; returns the previous one."""
+    f = lib().onellm_p2p_two_shot_bytes
+    f.restype = C.c_longlong
+    return int(f(C.c_longlong(nbytes)))
+
+
 class P2p:
     """The peer-memory all-reduce on its own (one object per process / GPU)."""
 

@@ -265,10 +265,18 @@ __device__ __forceinline__ float warp_max(float v)
 // finished an output element pushes it, as one 8-byte word {two fp16 values, sequence number}, into this
 // rank's slot on every peer, then waits for the peers' words of the same element in its own memory and
 // adds them in rank order.  world <= 1: not in use.
+// two_shot (large messages on many ranks): token row t belongs to rank t % world.  Every rank sends its partial
+// of a row to the row's owner only; the owner adds the partials in rank order, the residual and the bias, stores
+// the result and sends it, again as {two fp16 values, sequence number}, to every peer's `final` buffer; the
+// others store what they receive.  Same arithmetic, same bits as the one-shot form, 2 (world-1)/world of a
+// message per rank on the wire instead of (world-1) messages, at the price of a second hop.
 constexpr int kTpMaxBlocks = 1024;  // sequence counters available to one launch
 struct TpEpilogue {
     uint2* push[8];        // this rank's slot in the receive buffer of rank r (entry of the own rank unused)
     const uint2* mine;     // this rank's receive buffer of this call: [world][slot_words]
+    uint2* final_push[8];  // two_shot: the final-value buffer of rank r for this call
+    const uint2* final_mine;
+    int two_shot;
     size_t slot_words;
     int* counters;         // one sequence counter per thread block of the launch
     int* error;            // set when a bounded wait gave up

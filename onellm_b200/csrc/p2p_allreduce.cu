@@ -43,6 +43,8 @@ constexpr long long kP2pWaitCycles = 2000LL * 1000 * 1000;  // a wait for a peer
 //   [kCtlBytes]    send buffer 0, send buffer 1 (max_elems halfs each; written by this rank's projections)
 //   [..]           receive buffers [2][world][max_elems / 2] of 8-byte words {half2 data, sequence number},
 //                  slot [which][r] written by rank r
+//   [..]           final-value buffers [2][max_elems / 2] of the same words (two-shot form of the projections'
+//                  exchange: element e written by the rank that owns its token row)
 struct P2pControl {
     int counters[kP2pMaxBlocks];
     int error;
@@ -167,6 +169,8 @@ struct P2pComm {
         return reinterpret_cast<uint2*>(static_cast<char*>(base) + kCtlBytes + 2 * send_bytes()) +
                ((size_t)which * world + src) * slot_words();
     }
+    // final-value buffer [which] (two-shot exchange) inside the block that starts at `base`
+    uint2* final_slot(void* base, int which) const { return recv_slot(base, 2, 0) + (size_t)which * slot_words(); }
     void* local = nullptr;                    // this rank's block
     void* mapped[kP2pMaxWorld] = {};          // every rank's block in this process's address space
     bool connected = false;
@@ -189,7 +193,7 @@ extern "C" int onellm_p2p_create(int rank, int world, size_t max_elems, onellm_p
     c->rank = rank;
     c->world = world;
     c->max_elems = max_elems;
-    c->block_bytes = kCtlBytes + 2 * c->send_bytes() + (size_t)2 * world * c->slot_words() * sizeof(uint2);
+    c->block_bytes = kCtlBytes + 2 * c->send_bytes() + (size_t)2 * (world + 1) * c->slot_words() * sizeof(uint2);
     cudaError_t e = cudaGetDevice(&c->device);
     if (e == cudaSuccess) e = cudaMalloc(&c->local, c->block_bytes);
     if (e == cudaSuccess) e = cudaMemset(c->local, 0, c->block_bytes);
@@ -264,6 +268,8 @@ extern "C" int onellm_p2p_allreduce_add(onellm_p2p* h, int dtype, int which, voi
 }
 
 namespace onellm {
+// bytes a rank would put on the wire in the one-shot form from which the projections' exchange goes two-shot
+static long long g_two_shot_bytes = 3ll << 20;
 // skinny_gemm_staged.cu
 cudaError_t skinny_kn_staged_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K, bool dual,
                                       cudaStream_t st, const __half* resid, const __half* bias, float rms_eps, const TpEpilogue* tp);
@@ -289,6 +295,12 @@ extern "C" int onellm_p2p_gemm_allreduce_add(onellm_p2p* h, int dtype, int which
     TpEpilogue tp = {};
     for (int r = 0; r < c->world; r++) tp.push[r] = c->recv_slot(c->mapped[r], which, c->rank);
     tp.mine = c->recv_slot(c->local, which, 0);
+    for (int r = 0; r < c->world; r++) tp.final_push[r] = c->final_slot(c->mapped[r], which);
+    tp.final_mine = c->final_slot(c->local, which);
+    // one-shot moves (world - 1) tagged copies of the message per rank, two-shot 2 (world - 1) / world of one over
+    // two hops: worth it for the 64-token messages of the 13B shape on 4 ranks (7.94 -> 7.58 ms per step) and more,
+    // not for a batch of 8, and never on 2 ranks (the same bytes over two hops)
+    tp.two_shot = (c->world > 2 || g_two_shot_bytes == 0) && (long long)(c->world - 1) * M * N * 4 >= g_two_shot_bytes ? 1 : 0;
     tp.slot_words = c->slot_words();
     P2pControl* ctl = static_cast<P2pControl*>(c->local);
     tp.counters = ctl->gemm_counters;
@@ -312,6 +324,13 @@ extern "C" int onellm_p2p_gemm_allreduce_add(onellm_p2p* h, int dtype, int which
     }
     ONELLM_CUDA(e);
     return ONELLM_OK;
+}
+
+extern "C" long long onellm_p2p_two_shot_bytes(long long bytes)
+{
+    const long long before = g_two_shot_bytes;
+    if (bytes >= 0) g_two_shot_bytes = bytes;
+    return before;
 }
 
 extern "C" int onellm_p2p_error(onellm_p2p* h)

@@ -53,7 +53,9 @@ __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& c
     const int per_rank = (((MP * kBN + KS - 1) / KS) + 1) & ~1;
     const int e_begin = rank * per_rank, e_end = min(e_begin + per_rank, MP * kBN);
     const long long t_start = clock64();
-    for (int e = e_begin + 2 * tid; e < e_end; e += 2 * NT) {
+    // The value this block contributes to elements (tok, c) and (tok, c + 1): the K ranges of the cluster added in rank
+    // order, the RMS scale, SwiGLU.  False when the pair lies outside the matrix.
+    auto partial = [&](int e, float& v0, float& v1) {
         const int tok = e / kBN, c = e % kBN;
         // all remote loads are issued before the first is used (a cluster has at most 8 ranks): summing as
         // they are requested would pay one distributed-shared-memory round trip per rank
@@ -80,60 +82,118 @@ __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& c
             s1.y += p1[r].y;
             ss += ps[r];
         }
-        if (tok < M && n0 + c < N) {  // N is even: the second column is inside too
-            if (!FUSED && ep.rms) {
-                const float inv = rsqrtf(ss / (float)K + ep.rms_eps);
-                s0.x *= inv;
-                s0.y *= inv;
-                s1.x *= inv;
-                s1.y *= inv;
-            }
-            float v0 = DUAL ? (s0.x / (1.0f + __expf(-s0.x))) * s1.x : s0.x;
-            float v1 = DUAL ? (s0.y / (1.0f + __expf(-s0.y))) * s1.y : s0.y;
-            const size_t idx = (size_t)tok * N + n0 + c;
-            if (tp) {
-                // push this rank's value of the two elements to every peer, then gather theirs
-                const __half2 own = __floats2half2_rn(v0, v1);
-                const uint32_t word = *reinterpret_cast<const uint32_t*>(&own);
-#pragma unroll
-                for (int r = 0; r < 8; r++)
-                    if (r < ep.tp.world && r != ep.tp.rank)
-                        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(ep.tp.push[r] + idx / 2), "r"(word), "r"(seq)
-                                     : "memory");
-                v0 = v1 = 0.f;
-#pragma unroll
-                for (int r = 0; r < 8; r++)
-                    if (r < ep.tp.world) {
-                        uint32_t w = word;
-                        if (r != ep.tp.rank) {
-                            const uint2* src = ep.tp.mine + (size_t)r * ep.tp.slot_words + idx / 2;
-                            uint32_t got;
-                            for (;;) {
-                                asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(w), "=r"(got) : "l"(src) : "memory");
-                                if (got == seq) break;
-                                if (clock64() - t_start > 2000LL * 1000 * 1000) {  // about a second: give up, say so, go on
-                                    atomicExch(ep.tp.error, 1);
-                                    break;
-                                }
-                            }
-                        }
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-                        v0 += f.x;
-                        v1 += f.y;
-                    }
-            }
-            if (!FUSED && ep.resid) {
-                const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(ep.resid + idx));
-                v0 += rr.x;
-                v1 += rr.y;
-                if (ep.bias) {
-                    const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(ep.bias + n0 + c));
-                    v0 += bb.x;
-                    v1 += bb.y;
-                }
-            }
-            *reinterpret_cast<__half2*>(y + idx) = __floats2half2_rn(v0, v1);
+        if (!(tok < M && n0 + c < N)) return false;  // N is even: the second column is inside too
+        if (!FUSED && ep.rms) {
+            const float inv = rsqrtf(ss / (float)K + ep.rms_eps);
+            s0.x *= inv;
+            s0.y *= inv;
+            s1.x *= inv;
+            s1.y *= inv;
         }
+        v0 = DUAL ? (s0.x / (1.0f + __expf(-s0.x))) * s1.x : s0.x;
+        v1 = DUAL ? (s0.y / (1.0f + __expf(-s0.y))) * s1.y : s0.y;
+        return true;
+    };
+    // one bounded poll of a tagged word: returns the data word once it carries this call's sequence number
+    auto await = [&](const uint2* src) {
+        uint32_t w, got;
+        for (;;) {
+            asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(w), "=r"(got) : "l"(src) : "memory");
+            if (got == seq) break;
+            if (clock64() - t_start > 2000LL * 1000 * 1000) {  // about a second: give up, say so, go on
+                atomicExch(ep.tp.error, 1);
+                break;
+            }
+        }
+        return w;
+    };
+    auto send = [&](uint2* dst, uint32_t w) {
+        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(dst), "r"(w), "r"(seq) : "memory");
+    };
+    // this rank's fp16 partial `word` of a pair -> the partials of all ranks added in rank order
+    auto gather = [&](size_t idx, uint32_t word, float& v0, float& v1) {
+        v0 = v1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; r++)
+            if (r < ep.tp.world) {
+                const uint32_t w = r == ep.tp.rank ? word : await(ep.tp.mine + (size_t)r * ep.tp.slot_words + idx / 2);
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+                v0 += f.x;
+                v1 += f.y;
+            }
+    };
+    // residual and bias, then the store; returns what was stored
+    auto finish = [&](size_t idx, int c, float v0, float v1) {
+        if (!FUSED && ep.resid) {
+            const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(ep.resid + idx));
+            v0 += rr.x;
+            v1 += rr.y;
+            if (ep.bias) {
+                const float2 bb = __half22float2(*reinterpret_cast<const __half2*>(ep.bias + n0 + c));
+                v0 += bb.x;
+                v1 += bb.y;
+            }
+        }
+        const __half2 out = __floats2half2_rn(v0, v1);
+        *reinterpret_cast<__half2*>(y + idx) = out;
+        return *reinterpret_cast<const uint32_t*>(&out);
+    };
+
+    if (tp && ep.tp.two_shot) {
+        // Three passes, so that the two hops of all of a thread's pairs overlap: (1) every partial of a row that
+        // belongs to another rank goes to that rank; (2) the rows of this rank: gather, finish, store, and the
+        // finished value to everybody; (3) the other rows: store what their owners sent.
+        constexpr int kPairs = (MP * kBN / 2 + NT - 1) / NT;  // pairs a thread handles at most (K split of one)
+        uint32_t mine[kPairs];
+        unsigned valid = 0u;  // kPairs <= 32
+        static_assert(kPairs <= 32, "pair bookkeeping is one bit per pair");
+        int it = 0;
+        for (int e = e_begin + 2 * tid; e < e_end; e += 2 * NT, it++) {
+            float v0, v1;
+            if (!partial(e, v0, v1)) continue;
+            const int tok = e / kBN, c = e % kBN;
+            const __half2 own = __floats2half2_rn(v0, v1);
+            mine[it] = *reinterpret_cast<const uint32_t*>(&own);
+            valid |= 1u << it;
+            const int owner = tok % ep.tp.world;
+            if (owner != ep.tp.rank) send(ep.tp.push[owner] + ((size_t)tok * N + n0 + c) / 2, mine[it]);
+        }
+        it = 0;
+        for (int e = e_begin + 2 * tid; e < e_end; e += 2 * NT, it++) {
+            const int tok = e / kBN, c = e % kBN;
+            if (!((valid >> it) & 1u) || tok % ep.tp.world != ep.tp.rank) continue;
+            const size_t idx = (size_t)tok * N + n0 + c;
+            float v0, v1;
+            gather(idx, mine[it], v0, v1);
+            const uint32_t w = finish(idx, c, v0, v1);
+#pragma unroll
+            for (int r = 0; r < 8; r++)
+                if (r < ep.tp.world && r != ep.tp.rank) send(ep.tp.final_push[r] + idx / 2, w);
+        }
+        it = 0;
+        for (int e = e_begin + 2 * tid; e < e_end; e += 2 * NT, it++) {
+            const int tok = e / kBN, c = e % kBN;
+            if (!((valid >> it) & 1u) || tok % ep.tp.world == ep.tp.rank) continue;
+            const size_t idx = (size_t)tok * N + n0 + c;
+            *reinterpret_cast<uint32_t*>(y + idx) = await(ep.tp.final_mine + idx / 2);
+        }
+        return;
+    }
+    for (int e = e_begin + 2 * tid; e < e_end; e += 2 * NT) {
+        float v0, v1;
+        if (!partial(e, v0, v1)) continue;
+        const int tok = e / kBN, c = e % kBN;
+        const size_t idx = (size_t)tok * N + n0 + c;
+        if (tp) {
+            // one-shot: this rank's value of the two elements to every peer, then theirs
+            const __half2 own = __floats2half2_rn(v0, v1);
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(&own);
+#pragma unroll
+            for (int r = 0; r < 8; r++)
+                if (r < ep.tp.world && r != ep.tp.rank) send(ep.tp.push[r] + idx / 2, word);
+            gather(idx, word, v0, v1);
+        }
+        (void)finish(idx, c, v0, v1);
     }
 }
 

@@ -9,7 +9,7 @@ import pytest
 
 from conftest import rel_err
 
-HF = dict(num_attention_heads=4, num_key_value_heads=2, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+HF = dict(num_attention_heads=4, num_key_value_heads=2, hidden_size=256, intermediate_size=160, num_hidden_layers=2,
           vocab_size=120, max_position_embeddings=64, rope_theta=10000.0, rms_norm_eps=1e-5, bos_token_id=1, eos_token_id=2,
           attention_bias=False, _name_or_path="toy-llama")
 
@@ -116,7 +116,7 @@ def test_converted_checkpoint_gives_the_checkpoints_logits_through_the_oracle(tm
     d, sd, cfg = _checkpoint(tmp_path, bias=bias, tied=tied, sharded=sharded)
     out = os.path.join(str(tmp_path), "converted")
     section = convert(d, out, dtype, log=lambda *_: None)
-    assert section["head_size"] == "16" and section["attention_bias"] == str(bias) and section["weight_data_type"] == dtype
+    assert section["head_size"] == "64" and section["attention_bias"] == str(bias) and section["weight_data_type"] == dtype
     import configparser
     cp = configparser.ConfigParser()
     cp.read(os.path.join(out, "config.ini"))
@@ -150,7 +150,7 @@ def test_converter_refuses_what_it_does_not_cover(tmp_path):
     with pytest.raises(ValueError):
         convert(d, os.path.join(str(tmp_path), "o"), "fp16", log=lambda *_: None)
     with open(os.path.join(d, "config.json"), "w") as f:
-        json.dump(dict(cfg, intermediate_size=100), f)  # does not match the tensors
+        json.dump(dict(cfg, intermediate_size=96), f)  # does not match the tensors
     with pytest.raises(ValueError):
         convert(d, os.path.join(str(tmp_path), "o2"), "fp16", log=lambda *_: None)
 

@@ -104,6 +104,44 @@ def _p2p_worker(rank, size, port, q):
     everyone = [None] * size
     dist.all_gather_object(everyone, resid2.cpu())
     ok = ok and fused_err < 2e-3 and all(torch.equal(everyone[0], t) for t in everyone)   # bit-identical on every rank
+    # the two-shot form of the same exchange (partials to the owner of the token row, finished values back): the same
+    # ten calls from the same residual give the same bits; then 64 tokens, which the tcgen05 projection kernel takes
+    before = ob.p2p_two_shot_bytes(0)
+    resid3 = resid0.cuda()
+    for i, per_rank in enumerate(xs):
+        which = i % 2
+        comm.gemm_allreduce_add(which, per_rank[rank].cuda(), d_W, resid3, d_bias if which == 0 else None, rows, N, K)
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(resid3, resid2)
+    rows64 = 64
+    comm64 = ob.P2p(rank, size, rows64 * h)
+    handles = [None] * size
+    dist.all_gather_object(handles, comm64.handle())
+    comm64.connect(handles)
+    dist.barrier()
+    x64 = [[torch.randn(rows64, K, generator=gen).half() for _ in range(size)] for _ in range(4)]
+    r64 = torch.randn(rows64, N, generator=gen).half()
+    outs = []
+    for form in (1 << 40, 0):  # one-shot, two-shot
+        ob.p2p_two_shot_bytes(form)
+        res = r64.cuda()
+        for i, per_rank in enumerate(x64):
+            comm64.gemm_allreduce_add(i % 2, per_rank[rank].cuda(), d_W, res, d_bias if i % 2 == 0 else None, rows64, N, K)
+        torch.cuda.synchronize()
+        outs.append(res.cpu())
+    ob.p2p_two_shot_bytes(before)
+    want64 = r64.float()
+    for i, per_rank in enumerate(x64):
+        tot = torch.zeros(rows64, N)
+        for r in range(size):
+            tot += (per_rank[r].float() @ Ws[r].float()).half().float()
+        want64 = (tot + want64 + (bias.float() if i % 2 == 0 else 0.0)).half().float()
+    err64 = float((outs[0].float() - want64).abs().max() / want64.abs().max())
+    everyone = [None] * size
+    dist.all_gather_object(everyone, outs[1])
+    ok = ok and err64 < 2e-3 and torch.equal(outs[0], outs[1]) and all(torch.equal(everyone[0], t) for t in everyone)
+    ok = ok and comm64.error() == 0
+    comm64.close()
     first_err = comm.error()
     dist.barrier()
     # a call the last rank never joins: the others give up after about a second and say so
@@ -172,7 +210,7 @@ def test_p2p_allreduce_add_bit_exact_and_bounded_wait(ob, cuda):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    size = 2
+    size = 4 if torch.cuda.device_count() >= 4 else 2  # four ranks where the box has them: owners that are not neighbours
     procs = [ctx.Process(target=_p2p_worker, args=(r, size, port, q)) for r in range(size)]
     for p in procs:
         p.start()
