@@ -239,6 +239,12 @@ ONELLM_API int onellm_gemm_plan_override(int N, int K, int dual, int k_split, in
  * tokens on the mma.sync one (default 33).  Sets the threshold (min_tokens >= 1; 65 or more: never) and returns
  * the value it had; min_tokens <= 0 only queries.  A tuning aid like the two calls above. */
 ONELLM_API int onellm_gemm_tc_min_tokens(int min_tokens);
+
+/* Tuning aid: whether the tcgen05 weight-streaming kernel may give a block 256 output columns instead of 128
+ * (single weight, no tensor-parallel exchange, at least 512 columns; the activation tile of a stage then serves twice
+ * the weight bytes).  Default 1.  Returns the previous value; a negative argument only reads it. */
+ONELLM_API int onellm_gemm_tc_wide(int enabled);
+
 /* The same kind of aid for the fp16 decode attention (head size 64 / 128): forces the thread blocks per SM (1..3,
  * which fixes the depth of the per-warp rings) and / or the number of row ranges a (sequence, head) pair is split
  * into (1..16) for every later launch in this process; 0 leaves the choice to the planner. */

@@ -115,6 +115,11 @@ def decode_attn_merged(dtype, q, k, v, q_stride_b, k_stride_b, v_stride_b, bias_
         C.c_long(out_stride_b), _p(workspace), C.c_size_t(workspace_bytes), _p(tickets), _stream(stream)))
 
 
+def gemm_tc_wide(enabled=-1):
+    """Tuning aid: 256-column blocks in the tcgen05 weight-streaming kernel (default on); returns the previous setting."""
+    return int(lib().onellm_gemm_tc_wide(C.c_int(int(enabled))))
+
+
 def decode_attn_plan_override(blocks_per_sm=0, splits=0):
     """Tuning aid: fixes the tensor-core decode attention's blocks per SM (1..3) and split count (1..16); 0 = planner."""
     _check(lib().onellm_decode_attn_plan_override(C.c_int(blocks_per_sm), C.c_int(splits)))

@@ -32,15 +32,18 @@ struct EpilogueArgs {
 // `red` holds this block's partial tile as [NW][MP][kRedLd] floats followed by MP partial sums of squares (used
 // when ep.rms is set); the blocks of the cluster (rank = blockIdx.y of gridDim.y) hold the other K ranges of the
 // same tile.  Sums them in rank order and finishes the tile; every thread of the block (NT of them) calls it.
-template <int MP, bool DUAL, bool FUSED, int NT>
+// WIDE (tcgen05 kernel, no tensor-parallel exchange): the second half of `red` is not a second weight but the next
+// 128 output columns of the same weight (a block owns 256 columns and reads its activations once for both).
+template <int MP, bool DUAL, bool FUSED, int NT, bool WIDE = false>
 __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& cluster, __half* y, int M, int N, int K, int n0,
                                                 const EpilogueArgs& ep)
 {
-    constexpr int NW = DUAL ? 2 : 1;
+    static_assert(!(DUAL && WIDE), "two weights or two column tiles, not both");
+    constexpr int NW = (DUAL || WIDE) ? 2 : 1;
     const int KS = gridDim.y, rank = blockIdx.y, tid = threadIdx.x;
     // tensor parallel: this block's sequence number for the call (blocks pair up by index across the ranks)
     __shared__ uint32_t s_seq;
-    const bool tp = !FUSED && ep.tp.world > 1;
+    const bool tp = !FUSED && !WIDE && ep.tp.world > 1;
     if (tp && tid == 0) {
         int* ctr = ep.tp.counters + blockIdx.y * gridDim.x + blockIdx.x;
         const int n = *ctr + 1;
@@ -55,7 +58,7 @@ __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& c
     const long long t_start = clock64();
     // The value this block contributes to elements (tok, c) and (tok, c + 1): the K ranges of the cluster added in rank
     // order, the RMS scale, SwiGLU.  False when the pair lies outside the matrix.
-    auto partial = [&](int e, float& v0, float& v1) {
+    auto partial = [&](int e, float& v0, float& v1, float& w0, float& w1) {
         const int tok = e / kBN, c = e % kBN;
         // all remote loads are issued before the first is used (a cluster has at most 8 ranks): summing as
         // they are requested would pay one distributed-shared-memory round trip per rank
@@ -68,7 +71,7 @@ __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& c
             if (r < KS) {
                 const float* peer = cluster.map_shared_rank(red, r);
                 p0[r] = make_float2(peer[tok * kRedLd + c], peer[tok * kRedLd + c + 1]);
-                if (DUAL) p1[r] = make_float2(peer[(MP + tok) * kRedLd + c], peer[(MP + tok) * kRedLd + c + 1]);
+                if (NW == 2) p1[r] = make_float2(peer[(MP + tok) * kRedLd + c], peer[(MP + tok) * kRedLd + c + 1]);
                 if (!FUSED && ep.rms) ps[r] = peer[NW * MP * kRedLd + tok];
             }
         }
@@ -92,6 +95,8 @@ __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& c
         }
         v0 = DUAL ? (s0.x / (1.0f + __expf(-s0.x))) * s1.x : s0.x;
         v1 = DUAL ? (s0.y / (1.0f + __expf(-s0.y))) * s1.y : s0.y;
+        w0 = s1.x;  // WIDE: the same pair 128 columns further
+        w1 = s1.y;
         return true;
     };
     // one bounded poll of a tagged word: returns the data word once it carries this call's sequence number
@@ -149,8 +154,8 @@ __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& c
         static_assert(kPairs <= 32, "pair bookkeeping is one bit per pair");
         int it = 0;
         for (int e = e_begin + 2 * tid; e < e_end; e += 2 * NT, it++) {
-            float v0, v1;
-            if (!partial(e, v0, v1)) continue;
+            float v0, v1, w0, w1;
+            if (!partial(e, v0, v1, w0, w1)) continue;
             const int tok = e / kBN, c = e % kBN;
             const __half2 own = __floats2half2_rn(v0, v1);
             mine[it] = *reinterpret_cast<const uint32_t*>(&own);
@@ -180,10 +185,11 @@ __device__ __forceinline__ void splitk_epilogue(float* red, cg::cluster_group& c
         return;
     }
     for (int e = e_begin + 2 * tid; e < e_end; e += 2 * NT) {
-        float v0, v1;
-        if (!partial(e, v0, v1)) continue;
+        float v0, v1, w0, w1;
+        if (!partial(e, v0, v1, w0, w1)) continue;
         const int tok = e / kBN, c = e % kBN;
         const size_t idx = (size_t)tok * N + n0 + c;
+        if (WIDE && n0 + kBN + c < N) (void)finish(idx + kBN, c + kBN, w0, w1);
         if (tp) {
             // one-shot: this rank's value of the two elements to every peer, then theirs
             const __half2 own = __floats2half2_rn(v0, v1);

@@ -36,15 +36,18 @@ constexpr int kSkWTile = 2 * kSkWChunk;    // 16 KB: 128 weight columns x 64 k
 constexpr int kSkXTile = kSkTok * kSkBK * 2;  // 8 KB: 64 tokens x 64 k
 constexpr int kSkBarBytes = 256;
 
-template <bool DUAL>
+// WIDE: one weight, 256 output columns per block (the second 128 where DUAL has its second weight): the activation
+// tile of a stage, a third of a narrow block's ring, then serves twice the weight bytes.
+template <bool DUAL, bool WIDE>
 __global__ void __launch_bounds__(kSkThreads)
 skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                  const __grid_constant__ CUtensorMap map_x, __half* y, int M, int N, int K, int stages_per_block, int nst,
                  const EpilogueArgs ep)
 {
-    constexpr int NW = DUAL ? 2 : 1;
+    constexpr int NW = (DUAL || WIDE) ? 2 : 1;
+    constexpr int kTileCols = WIDE ? 2 * kBN : kBN;
     constexpr int STAGE = NW * kSkWTile + kSkXTile;
-    constexpr uint32_t kCols = DUAL ? 128u : 64u;  // tensor-memory columns: gate at 0, up at 64
+    constexpr uint32_t kCols = NW == 2 ? 128u : 64u;  // tensor-memory columns: gate (or the first 128 outputs) at 0, up (the next 128) at 64
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)nst * STAGE);
@@ -52,7 +55,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = blockIdx.y;
-    const int n0 = blockIdx.x * kBN;
+    const int n0 = blockIdx.x * kTileCols;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_stages = (K + kSkBK - 1) / kSkBK;
     const int s_begin = min(rank * stages_per_block, total_stages);
@@ -89,6 +92,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_consta
                 for (int c = 0; c < 2; c++) {
                     tma_load_2d(dst + c * kSkWChunk, &map_w0, n0 + 64 * c, k0, full0 + 8 * s);
                     if (DUAL) tma_load_2d(dst + kSkWTile + c * kSkWChunk, &map_w1, n0 + 64 * c, k0, full0 + 8 * s);
+                    if (WIDE) tma_load_2d(dst + kSkWTile + c * kSkWChunk, &map_w0, n0 + kBN + 64 * c, k0, full0 + 8 * s);
                 }
             };
             auto load_x = [&](int it) {
@@ -129,7 +133,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_consta
                     // activations: rows of 128 bytes, groups of 8 rows 1 KB apart, 16 k = 32 bytes further in the row
                     const uint64_t bdesc = umma_desc(x_addr + kk * 32, 16, 1024);
                     umma_f16(tmem_base, umma_desc(w_addr + kk * 2048, kSkWChunk, 1024), bdesc, idesc, (it > 0 || kk > 0) ? 1u : 0u);
-                    if (DUAL)
+                    if (NW == 2)
                         umma_f16(tmem_base + 64u, umma_desc(w_addr + kSkWTile + kk * 2048, kSkWChunk, 1024), bdesc, idesc,
                                  (it > 0 || kk > 0) ? 1u : 0u);
                 }
@@ -201,7 +205,7 @@ skinny_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_consta
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kCols) : "memory");
     }
-    splitk_epilogue<kSkTok, DUAL, false, kSkThreads>(reinterpret_cast<float*>(smem), cluster, y, M, N, K, n0, ep);
+    splitk_epilogue<kSkTok, DUAL, false, kSkThreads, WIDE>(reinterpret_cast<float*>(smem), cluster, y, M, N, K, n0, ep);
     cluster.sync();  // peers may still be reading this block's tile
 }
 
@@ -215,12 +219,26 @@ struct TcPlan {
 bool plan_override_lookup(int N, int K, bool dual, int* ks, int* nst);  // skinny_gemm_staged.cu (onellm_gemm_plan_override)
 
 static int g_tc_min_tokens = 33;  // projections of at least this many tokens take this kernel (onellm_gemm_tc_min_tokens)
+static int g_tc_wide = 1;         // 256-column blocks where they apply (onellm_gemm_tc_wide)
 
-template <bool DUAL>
+// Shapes with a tuned plan of the narrow kernel (see plan_tc).
+struct TunedTc {
+    int N, K;
+    bool dual;
+    int ks, nst;
+};
+static const TunedTc kTunedTc[] = {
+    {7680, 5120, false, 5, 3}, {5120, 2560, false, 5, 4}, {5120, 6912, false, 4, 4},                               // 2 ways
+    {3840, 5120, false, 4, 6}, {5120, 1280, false, 5, 3}, {3456, 5120, true, 4, 4}, {5120, 3456, false, 6, 4},  // 4 ways
+    {1920, 5120, false, 8, 6}, {5120, 640, false, 5, 3},  {1728, 5120, true, 8, 4}, {5120, 1728, false, 4, 4},  // 8 ways
+};
+
+template <bool DUAL, bool WIDE>
 static TcPlan plan_tc(int N, int K, bool tp)
 {
-    auto kern = skinny_tc_kernel<DUAL>;
-    constexpr int NW = DUAL ? 2 : 1;
+    auto kern = skinny_tc_kernel<DUAL, WIDE>;
+    constexpr int NW = (DUAL || WIDE) ? 2 : 1;
+    constexpr int kTileCols = WIDE ? 2 * kBN : kBN;
     constexpr size_t stage = (size_t)NW * kSkWTile + kSkXTile;
     constexpr size_t red = ((size_t)NW * kSkTok * kRedLd + kSkTok) * sizeof(float);
     constexpr size_t cap = 226 * 1024;  // the kernel also has 1 KB of static shared memory
@@ -234,10 +252,10 @@ static TcPlan plan_tc(int N, int K, bool tp)
         return e != cudaSuccess ? e : prefer_max_shared((const void*)kern);
     });
     if (plan.status != cudaSuccess) return plan;
-    const int col_tiles = (N + kBN - 1) / kBN;
+    const int col_tiles = (N + kTileCols - 1) / kTileCols;
     const int total_stages = (K + kSkBK - 1) / kSkBK;
     int oks = 0, onst = 0;
-    if (!tp && plan_override_lookup(N, K, DUAL, &oks, &onst)) {  // tuning aid; never cached
+    if (!tp && !WIDE && plan_override_lookup(N, K, DUAL, &oks, &onst)) {  // tuning aid; never cached
         const int per = oks >= 1 ? (total_stages + oks - 1) / oks : 0;
         if (oks < 1 || oks > 8 || oks > total_stages || per * (oks - 1) >= total_stages || onst < 2 || onst > max_nst) {
             plan.status = cudaErrorInvalidValue;
@@ -297,18 +315,8 @@ static TcPlan plan_tc(int N, int K, bool tp)
     // for the 13B shape split 2, 4 and 8 ways at 33-64 tokens: a ring of 3-6 stages leaves room for two blocks per
     // SM, which then hide each other's start-up and reduction, and allows a wider K split.  Used when all their
     // blocks are resident at once (which the tensor-parallel epilogue needs in any case).
-    struct Tuned {
-        int N, K;
-        bool dual;
-        int ks, nst;
-    };
-    static const Tuned kTuned[] = {
-        {7680, 5120, false, 5, 3}, {5120, 2560, false, 5, 4}, {5120, 6912, false, 4, 4},                               // 2 ways
-        {3840, 5120, false, 4, 6}, {5120, 1280, false, 5, 3}, {3456, 5120, true, 4, 4}, {5120, 3456, false, 6, 4},  // 4 ways
-        {1920, 5120, false, 8, 6}, {5120, 640, false, 5, 3},  {1728, 5120, true, 8, 4}, {5120, 1728, false, 4, 4},  // 8 ways
-    };
-    for (const Tuned& t : kTuned) {
-        if (t.N != N || t.K != K || t.dual != DUAL || t.nst > max_nst) continue;
+    for (const TunedTc& t : kTunedTc) {
+        if (WIDE || t.N != N || t.K != K || t.dual != DUAL || t.nst > max_nst) continue;
         const int per = (total_stages + t.ks - 1) / t.ks;
         if (t.ks > total_stages || per * (t.ks - 1) >= total_stages) continue;
         if (resident_clusters(t.ks, t.nst) >= col_tiles) return take(t.ks, t.nst);
@@ -346,7 +354,7 @@ static TcPlan plan_tc(int N, int K, bool tp)
     if (best_ks == 0) {
         // More column tiles than SMs (the LM head: 250 tiles).  A four-stage ring lets two blocks share an SM: one wave
         // instead of 1.7 (13B LM head at 64 tokens: 58.6 us instead of 85.9).
-        if (resident_clusters(1, 4) >= col_tiles) return take(1, 4);
+        if (!WIDE && resident_clusters(1, 4) >= col_tiles) return take(1, 4);
         // else no K split and several waves (not for the tensor-parallel epilogue, whose blocks wait for the blocks of
         // the same index on the other GPUs)
         if (tp) plan.status = cudaErrorInvalidConfiguration;
@@ -361,18 +369,19 @@ static TcPlan plan_tc(int N, int K, bool tp)
     return plan;
 }
 
-template <bool DUAL>
+template <bool DUAL, bool WIDE>
 static cudaError_t launch_tc(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K, const EpilogueArgs& ep,
                              cudaStream_t st)
 {
-    const TcPlan plan = plan_tc<DUAL>(N, K, ep.tp.world > 1);
+    constexpr int kTileCols = WIDE ? 2 * kBN : kBN;
+    const TcPlan plan = plan_tc<DUAL, WIDE>(N, K, ep.tp.world > 1);
     if (plan.status != cudaSuccess) return plan.status;
     CUtensorMap map_w0, map_w1, map_x;
     if (make_map(&map_w0, W0, (uint64_t)N, (uint64_t)K, kSkBK) != ONELLM_OK) return cudaErrorInvalidValue;
     map_w1 = map_w0;
     if (DUAL && make_map(&map_w1, W1, (uint64_t)N, (uint64_t)K, kSkBK) != ONELLM_OK) return cudaErrorInvalidValue;
     if (make_map(&map_x, x, (uint64_t)K, (uint64_t)M, kSkTok) != ONELLM_OK) return cudaErrorInvalidValue;
-    (void)prefer_max_shared((const void*)skinny_tc_kernel<DUAL>);
+    (void)prefer_max_shared((const void*)skinny_tc_kernel<DUAL, WIDE>);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -381,19 +390,19 @@ static cudaError_t launch_tc(const __half* x, const __half* W0, const __half* W1
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.gridDim = dim3((N + kBN - 1) / kBN, plan.ks, 1);
+    cfg.gridDim = dim3((N + kTileCols - 1) / kTileCols, plan.ks, 1);
     cfg.blockDim = dim3(kSkThreads);
     cfg.dynamicSmemBytes = plan.smem;
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     note_launch();
-    return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<DUAL>, map_w0, map_w1, map_x, y, M, N, K, plan.per_block, plan.nst, ep);
+    return cudaLaunchKernelEx(&cfg, skinny_tc_kernel<DUAL, WIDE>, map_w0, map_w1, map_x, y, M, N, K, plan.per_block, plan.nst, ep);
 }
 
 cudaError_t skinny_tc_plan_query(int N, int K, bool dual, int* ks, int* nst)
 {
-    const TcPlan p = dual ? plan_tc<true>(N, K, false) : plan_tc<false>(N, K, false);
+    const TcPlan p = dual ? plan_tc<true, false>(N, K, false) : plan_tc<false, false>(N, K, false);
     *ks = p.ks;
     *nst = p.nst;
     return p.status;
@@ -405,12 +414,28 @@ bool skinny_tc_takes(int M, int N, int K) { return M >= g_tc_min_tokens && M <= 
 cudaError_t skinny_tc_dispatch(const __half* x, const __half* W0, const __half* W1, __half* y, int M, int N, int K, const EpilogueArgs& ep,
                                cudaStream_t st)
 {
-    return W1 ? launch_tc<true>(x, W0, W1, y, M, N, K, ep, st) : launch_tc<false>(x, W0, nullptr, y, M, N, K, ep, st);
+    if (W1) return launch_tc<true, false>(x, W0, W1, y, M, N, K, ep, st);
+    // 256-column blocks for a single weight: not with the tensor-parallel exchange in the epilogue, not where a plan of
+    // the narrow kernel was tuned or is forced, and not where the narrow tiles outnumber the SMs (the LM head, which
+    // runs as one wave of two narrow blocks per SM)
+    bool wide = g_tc_wide != 0 && ep.tp.world <= 1 && N >= 4 * kBN && (N + kBN - 1) / kBN <= num_sms();
+    int oks = 0, onst = 0;
+    if (wide && plan_override_lookup(N, K, false, &oks, &onst)) wide = false;
+    for (const TunedTc& t : kTunedTc)
+        if (wide && t.N == N && t.K == K && !t.dual) wide = false;
+    return wide ? launch_tc<false, true>(x, W0, nullptr, y, M, N, K, ep, st) : launch_tc<false, false>(x, W0, nullptr, y, M, N, K, ep, st);
 }
 
 int skinny_tc_flag() { return tc_flag_read_clear(); }
 
 }  // namespace onellm
+
+extern "C" int onellm_gemm_tc_wide(int enabled)
+{
+    const int before = onellm::g_tc_wide;
+    if (enabled >= 0) onellm::g_tc_wide = enabled ? 1 : 0;
+    return before;
+}
 
 extern "C" int onellm_gemm_tc_min_tokens(int min_tokens)
 {

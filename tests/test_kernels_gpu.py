@@ -569,6 +569,9 @@ def test_gemm_f16_tensor_core_tiles(ob, cuda, orc, M, N, K, nk):
     (1000, 528, True, False, True),       # ragged in N and K
     (5120, 1728, False, False, True),     # 13B down_proj slices: tuned plans with two blocks per SM
     (5120, 3456, False, False, True),
+    (12288, 4096, False, True, False),    # 256-column blocks: 7B QKV behind the norm
+    (4096, 11008, False, False, True),    # 7B down_proj adding into the residual stream
+    (1160, 528, False, True, True),       # the last 256-column block has 128 + 8 columns, K is ragged
 ])
 def test_gemm_tensor_core_weight_streaming_kernel(ob, cuda, orc, M, N, K, dual, rms, resid):
     """The tcgen05 kernel for 17..64 tokens (forced from 17 tokens up here) against the oracle, and bit-identical to itself."""
