@@ -242,7 +242,8 @@ ONELLM_API int onellm_gemm_tc_min_tokens(int min_tokens);
 
 /* Tuning aid: whether the tcgen05 weight-streaming kernel may give a block 256 output columns instead of 128
  * (single weight, no tensor-parallel exchange, at least 512 columns; the activation tile of a stage then serves twice
- * the weight bytes).  Default 1.  Returns the previous value; a negative argument only reads it. */
+ * the weight bytes).  Default 1; 0: never; 2: also for the shapes that have a tuned plan of the 128-column form
+ * (for sweeps).  Returns the previous value; a negative argument only reads it. */
 ONELLM_API int onellm_gemm_tc_wide(int enabled);
 
 /* The same kind of aid for the fp16 decode attention (head size 64 / 128): forces the thread blocks per SM (1..3,
