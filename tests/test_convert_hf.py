@@ -129,6 +129,39 @@ def test_converted_checkpoint_gives_the_checkpoints_logits_through_the_oracle(tm
     assert rel_err(got, want) < 2e-5
 
 
+@pytest.mark.parametrize("fmt", ["pytorch_bin", "bf16_safetensors"])
+def test_converter_reads_the_other_checkpoint_formats(tmp_path, fmt):
+    """A single pytorch_model.bin, and safetensors holding bfloat16: the converted fp32 files equal the ones from the
+    fp32 safetensors checkpoint (bf16 after the rounding the checkpoint itself carries)."""
+    import torch
+    from onellm_b200.convert_hf import convert
+    d, sd, cfg = _checkpoint(tmp_path)
+    ref_out = os.path.join(str(tmp_path), "ref")
+    convert(d, ref_out, "fp32", log=lambda *_: None)
+    d2 = os.path.join(str(tmp_path), "other")
+    os.makedirs(d2)
+    with open(os.path.join(d2, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    if fmt == "pytorch_bin":
+        torch.save({k: torch.from_numpy(v) for k, v in sd.items()}, os.path.join(d2, "pytorch_model.bin"))
+        expect = lambda a: a
+    else:
+        from safetensors.torch import save_file
+        save_file({k: torch.from_numpy(v).to(torch.bfloat16) for k, v in sd.items()}, os.path.join(d2, "model.safetensors"))
+        expect = None
+    out = os.path.join(str(tmp_path), "out")
+    convert(d2, out, "fp32", log=lambda *_: None)
+    names = sorted(n for n in os.listdir(ref_out) if n != "config.ini")
+    assert names == sorted(n for n in os.listdir(out) if n != "config.ini") and len(names) == 3 + 7 * cfg["num_hidden_layers"]
+    for n in names:
+        a, b = np.fromfile(os.path.join(ref_out, n), np.float32), np.fromfile(os.path.join(out, n), np.float32)
+        if expect is not None:
+            assert np.array_equal(a, b), n
+        else:  # what bfloat16 keeps of the same values
+            want = torch.from_numpy(a).to(torch.bfloat16).float().numpy()
+            assert np.array_equal(want, b), n
+
+
 def test_interleave_rotary_rows_is_the_stated_permutation():
     from onellm_b200.convert_hf import interleave_rotary_rows
     heads, D = 3, 8
